@@ -115,22 +115,32 @@ class Cache:
         self.state_version = 0      # bumped by every change of lengths, pages or slots
         self.kv_groups: list[KVGroup] = []
         self.state_groups: list[StateGroup] = []
-        self._where: dict[int, tuple[str, int]] = {}
+        # entry -> its places, each (kind, group): one for most mixers, keys/values and a state for
+        # a mixer that keeps both
+        self._where: dict[int, list[tuple[str, int]]] = {}
         by_spec: dict[object, list[int]] = {}
         for entry, spec in sorted(specs.items()):
-            if spec is not None:
-                by_spec.setdefault(spec, []).append(entry)
+            if spec is None:
+                continue
+            several = list(spec) if isinstance(spec, (tuple, list)) else [spec]
+            kinds = [type(s) for s in several]
+            if kinds.count(KVSpec) > 1 or kinds.count(StateSpec) > 1:
+                raise TypeError(f"cache entry {entry}: at most one KVSpec and one StateSpec per entry, got {spec!r}")
+            for s in several:
+                by_spec.setdefault(s, []).append(entry)
         for spec, entries in by_spec.items():
             if isinstance(spec, KVSpec):
                 self.kv_groups.append(KVGroup(spec, entries, self.n_pages, page_size, dtype, device))
                 for e in entries:
-                    self._where[e] = ("kv", len(self.kv_groups) - 1)
+                    self._where.setdefault(e, []).append(("kv", len(self.kv_groups) - 1))
             elif isinstance(spec, StateSpec):
                 self.state_groups.append(StateGroup(spec, entries, self.max_seqs, device))
                 for e in entries:
-                    self._where[e] = ("state", len(self.state_groups) - 1)
+                    self._where.setdefault(e, []).append(("state", len(self.state_groups) - 1))
             else:
                 raise TypeError(f"unknown cache spec {spec!r}")
+        for places in self._where.values():
+            places.sort()        # keys and values before the state, whatever order the groups were made in
 
     # ---- sequences -----------------------------------------------------------------------
     def alloc_seq(self) -> int:
@@ -180,8 +190,13 @@ class Cache:
         return max((len(g.seq_pages.get(slot, ())) for g in self.kv_groups), default=0)
 
     # ---- a sequence as bytes --------------------------------------------------------------
-    def _entry_nbytes(self, entry: int, length: int) -> int:
-        kind, gi = self._where[entry]
+    def _places(self) -> list[tuple[int, str, int]]:
+        """(entry, kind, group) of everything the cache holds, in the order it is written out."""
+        return [(e, kind, gi) for e in sorted(self._where) for kind, gi in self._where[e]]
+
+    def _entry_nbytes(self, entry: int, length: int, kind: str | None = None, gi: int = 0) -> int:
+        if kind is None:
+            return sum(self._entry_nbytes(entry, length, k, g) for k, g in self._where[entry])
         if kind == "state":
             g = self.state_groups[gi]
             return int(np.prod(g.spec.shape, dtype=np.int64)) * g.data.element_size()
@@ -198,8 +213,7 @@ class Cache:
         out = [struct.pack("<Q", n)]
         raw = lambda t: t.contiguous().view(torch.uint8).cpu().numpy().tobytes()
         ps = self.page_size
-        for entry in sorted(self._where):
-            kind, gi = self._where[entry]
+        for entry, kind, gi in self._places():
             if kind == "state":
                 g = self.state_groups[gi]
                 out.append(raw(g.data[g.index[entry], slot].reshape(-1)))
@@ -236,9 +250,8 @@ class Cache:
             raise
         ps, o = self.page_size, 8
         buf = torch.frombuffer(bytearray(data), dtype=torch.uint8).to(self.device)
-        for entry in sorted(self._where):
-            kind, gi = self._where[entry]
-            nb = self._entry_nbytes(entry, n)
+        for entry, kind, gi in self._places():
+            nb = self._entry_nbytes(entry, n, kind, gi)
             if kind == "state":
                 g = self.state_groups[gi]
                 dst = g.data[g.index[entry], slot]
@@ -265,21 +278,21 @@ class Cache:
 
     # ---- views ---------------------------------------------------------------------------
     def group_of(self, entry: int) -> tuple[str, int] | None:
-        return self._where.get(entry)
+        """(kind, group) of the entry's first place (its keys and values, if it has any)."""
+        w = self._where.get(entry)
+        return w[0] if w else None
 
     def view(self, entry: int, writable: bool, tables: dict[int, torch.Tensor]) -> CacheView:
-        w = self._where.get(entry)
-        if w is None:
-            return CacheView(writable=writable, page_size=self.page_size)
-        kind, gi = w
-        if kind == "kv":
-            g = self.kv_groups[gi]
-            i = g.index[entry]
-            sp = g.spec
-            return CacheView(writable=writable, page_size=self.page_size, k=g.k_pool[i], v=g.v_pool[i],
-                             block_table=tables[gi])
-        g = self.state_groups[gi]
-        return CacheView(writable=writable, page_size=self.page_size, state=g.data[g.index[entry]])
+        view = CacheView(writable=writable, page_size=self.page_size)
+        for kind, gi in self._where.get(entry, ()):
+            if kind == "kv":
+                g = self.kv_groups[gi]
+                i = g.index[entry]
+                view.k, view.v, view.block_table = g.k_pool[i], g.v_pool[i], tables[gi]
+            else:
+                g = self.state_groups[gi]
+                view.state = g.data[g.index[entry]]
+        return view
 
     def check(self) -> None:
         """Bookkeeping invariants (used by tests): nothing lost, nothing held twice."""

@@ -101,11 +101,12 @@ def read_config_json(path: str) -> dict[str, Any]:
 
 
 def architecture_name(raw: dict[str, Any]) -> str:
-    """The name the registry is asked for: `architectures[0]`, else `model_type`."""
+    """The name the registry is asked for: `architectures[0]`, else `model_type`, else `architecture`."""
     archs = raw.get("architectures")
     if isinstance(archs, list) and archs and isinstance(archs[0], str):
         return archs[0]
-    mt = raw.get("model_type")
-    if isinstance(mt, str):
-        return mt
-    raise ConfigError("config.json: neither 'architectures' nor 'model_type' names the model")
+    for key in ("model_type", "architecture"):
+        mt = raw.get(key)
+        if isinstance(mt, str):
+            return mt
+    raise ConfigError("config.json: none of 'architectures', 'model_type' and 'architecture' names the model")

@@ -24,14 +24,14 @@
 #define ATT_RPW 8  // query vectors per warp at most: 32 / 4
 #define ATT_NEG (-1e30f)
 
-template <typename T, typename CT, int HDL>  // head_dim <= 32 * HDL
+template <typename T, typename CT, int HDL>  // value head size <= 32 * HDL (the key head size is free)
 __global__ void __launch_bounds__(32 * ATT_WARPS)
 attention_kernel(T* __restrict__ out, float* __restrict__ part, const T* __restrict__ q,
                  const CT* __restrict__ k_pool, const CT* __restrict__ v_pool,
                  const int* __restrict__ block_table, int bt_width,
                  const int* __restrict__ seq_slot, const int* __restrict__ seq_pos0,
                  const int* __restrict__ seq_qstart, const int* __restrict__ seq_qlen,
-                 const T* __restrict__ gate, int gate_stride, int nh, int nkv, int hd,
+                 const T* __restrict__ gate, int gate_stride, int nh, int nkv, int hd, int vd,
                  int page_size, int window, float scale, int QT, int HC, int n_splits) {
   extern __shared__ float sm[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -52,8 +52,8 @@ attention_kernel(T* __restrict__ out, float* __restrict__ part, const T* __restr
 
   float* q_s = sm;                 // [R][hd]
   float* k_s = q_s + R * hd;       // [32][hd + 1]
-  float* v_s = k_s + 32 * KS;      // [32][hd]
-  float* p_s = v_s + 32 * hd;      // [ATT_WARPS][32]
+  float* v_s = k_s + 32 * KS;      // [32][vd]
+  float* p_s = v_s + 32 * vd;      // [ATT_WARPS][32]
 
   if (slot < 0) {  // padding sequence: defined output, no cache access
     for (int r = warp; r < R; r += ATT_WARPS) {
@@ -62,11 +62,11 @@ attention_kernel(T* __restrict__ out, float* __restrict__ part, const T* __restr
       int h = kvh * G + hc * HC + j;
       size_t m = (size_t)q0 + row_lo + i;
       if (n_splits == 1) {
-        for (int d = lane; d < hd; d += 32) out[(m * nh + h) * hd + d] = from_f32<T>(0.f);
+        for (int d = lane; d < vd; d += 32) out[(m * nh + h) * vd + d] = from_f32<T>(0.f);
       } else {
-        float* pp = part + ((m * nh + h) * n_splits + split) * (size_t)(hd + 2);
+        float* pp = part + ((m * nh + h) * n_splits + split) * (size_t)(vd + 2);
         if (lane == 0) { pp[0] = ATT_NEG; pp[1] = 0.f; }
-        for (int d = lane; d < hd; d += 32) pp[2 + d] = 0.f;
+        for (int d = lane; d < vd; d += 32) pp[2 + d] = 0.f;
       }
     }
     return;
@@ -106,17 +106,19 @@ attention_kernel(T* __restrict__ out, float* __restrict__ part, const T* __restr
     const int key0 = tile * 32;
     const int page = block_table[(size_t)b * bt_width + key0 / page_size];
     const size_t base = (((size_t)(page < 0 ? 0 : page) * nkv + kvh) * page_size + key0 % page_size) * hd;
-    const size_t vbase = ((size_t)(page < 0 ? 0 : page) * nkv + kvh) * hd * page_size + key0 % page_size;
+    const size_t vbase = ((size_t)(page < 0 ? 0 : page) * nkv + kvh) * vd * page_size + key0 % page_size;
     __syncthreads();  // the previous tile has been consumed (and q_s is written, first time round)
     for (int idx = threadIdx.x; idx < 32 * hd; idx += blockDim.x) {
       int kk = idx / hd, d = idx - kk * hd;
-      float kv = 0.f, vv = 0.f;
-      if (page >= 0 && key0 + kk < kv_len) {  // beyond the sequence the pool holds stale bits
-        kv = to_f32(k_pool[base + idx]);
-        vv = to_f32(v_pool[vbase + (size_t)d * page_size + kk]);   // values are stored [dim][position]
-      }
+      float kv = 0.f;
+      if (page >= 0 && key0 + kk < kv_len) kv = to_f32(k_pool[base + idx]);  // beyond the sequence the pool holds stale bits
       k_s[kk * KS + d] = kv;
-      v_s[idx] = vv;
+    }
+    for (int idx = threadIdx.x; idx < 32 * vd; idx += blockDim.x) {
+      int d = idx / 32, kk = idx - d * 32;                         // values are stored [dim][position]
+      float vv = 0.f;
+      if (page >= 0 && key0 + kk < kv_len) vv = to_f32(v_pool[vbase + (size_t)d * page_size + kk]);
+      v_s[kk * vd + d] = vv;
     }
     __syncthreads();
 #pragma unroll
@@ -144,10 +146,10 @@ attention_kernel(T* __restrict__ out, float* __restrict__ part, const T* __restr
 #pragma unroll
       for (int jj = 0; jj < HDL; jj++) {
         const int d = lane + 32 * jj;
-        if (d < hd) {
+        if (d < vd) {
           float a = 0.f;
 #pragma unroll 8
-          for (int kk = 0; kk < 32; kk++) a += p_s[warp * 32 + kk] * v_s[kk * hd + d];
+          for (int kk = 0; kk < 32; kk++) a += p_s[warp * 32 + kk] * v_s[kk * vd + d];
           acc[ri][jj] = acc[ri][jj] * corr + a;
         }
       }
@@ -173,15 +175,15 @@ attention_kernel(T* __restrict__ out, float* __restrict__ part, const T* __restr
 #pragma unroll
       for (int jj = 0; jj < HDL; jj++) {
         const int d = lane + 32 * jj;
-        if (d < hd) out[(m * nh + h) * hd + d] = from_f32<T>(acc[ri][jj] * inv * g);
+        if (d < vd) out[(m * nh + h) * vd + d] = from_f32<T>(acc[ri][jj] * inv * g);
       }
     } else {
-      float* pp = part + ((m * nh + h) * n_splits + split) * (size_t)(hd + 2);
+      float* pp = part + ((m * nh + h) * n_splits + split) * (size_t)(vd + 2);
       if (lane == 0) { pp[0] = mx[ri]; pp[1] = l[ri]; }
 #pragma unroll
       for (int jj = 0; jj < HDL; jj++) {
         const int d = lane + 32 * jj;
-        if (d < hd) pp[2 + d] = acc[ri][jj];
+        if (d < vd) pp[2 + d] = acc[ri][jj];
       }
     }
   }
@@ -238,7 +240,7 @@ static int launch_attention(void* out, float* part, const void* q, const void* k
                             const void* v_pool, const int* block_table, int bt_width,
                             const int* seq_slot, const int* seq_pos0, const int* seq_qstart,
                             const int* seq_qlen, const void* gate, int gate_stride, int B, int nh,
-                            int nkv, int hd, int page_size, int window, float scale, int max_qlen,
+                            int nkv, int hd, int vd, int page_size, int window, float scale, int max_qlen,
                             int n_splits, cudaStream_t st) {
   const int G = nh / nkv;
   const int HC = G < 8 ? G : 8;
@@ -246,7 +248,7 @@ static int launch_attention(void* out, float* part, const void* q, const void* k
   if (QT > max_qlen) QT = max_qlen;
   const int R = QT * HC;
   const int n_hc = ceil_div(G, HC);
-  size_t smem = ((size_t)R * hd + 32 * (hd + 1) + 32 * hd + ATT_WARPS * 32) * sizeof(float);
+  size_t smem = ((size_t)R * hd + 32 * (hd + 1) + 32 * vd + ATT_WARPS * 32) * sizeof(float);
   auto kern = attention_kernel<T, CT, HDL>;
   static size_t smem_set = 0;
   if (smem > 48 * 1024 && smem > smem_set) {
@@ -258,43 +260,45 @@ static int launch_attention(void* out, float* part, const void* q, const void* k
   LEB_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "leb_attention: grid too large (%u, %u)", grid.y, grid.z);
   kern<<<grid, 32 * ATT_WARPS, smem, st>>>(
       (T*)out, part, (const T*)q, (const CT*)k_pool, (const CT*)v_pool, block_table, bt_width,
-      seq_slot, seq_pos0, seq_qstart, seq_qlen, (const T*)gate, gate_stride, nh, nkv, hd, page_size,
+      seq_slot, seq_pos0, seq_qstart, seq_qlen, (const T*)gate, gate_stride, nh, nkv, hd, vd, page_size,
       window, scale, QT, HC, n_splits);
   LEB_CHECK_LAUNCH("leb_attention");
   return 0;
 }
 
-// out, q: [M, nh*hd]; key pool [page][nkv][page_size][hd], value pool [page][nkv][hd][page_size];
-// part: float scratch of
-// M*nh*n_splits*(hd+2) elements, used when n_splits > 1 (then every sequence has one row).
+// q: [M, nh*hd]; out: [M, nh*vd]; key pool [page][nkv][page_size][hd], value pool
+// [page][nkv][vd][page_size] (vd <= 0: as wide as the keys); part: float scratch of
+// M*nh*n_splits*(vd+2) elements, used when n_splits > 1 (then every sequence has one row).
 LEB_API int leb_attention(void* out, float* part, const void* q, const void* k_pool,
                           const void* v_pool, int dtype, const int* block_table, int bt_width,
                           const int* seq_slot, const int* seq_pos0, const int* seq_qstart,
                           const int* seq_qlen, const void* gate, int gate_stride, int M, int B,
                           int nh, int nkv, int hd, int page_size, int window, float scale,
-                          int max_qlen, int n_splits, cudaStream_t st) {
+                          int max_qlen, int n_splits, int vd, cudaStream_t st) {
   if (M <= 0 || B <= 0) return 0;
+  if (vd <= 0) vd = hd;
+  LEB_REQUIRE(vd <= 256, "leb_attention: value head size %d outside 1..256", vd);
   LEB_REQUIRE(nkv > 0 && nh % nkv == 0, "leb_attention: %d heads do not divide into %d kv heads", nh, nkv);
   LEB_REQUIRE(hd >= 1 && hd <= 256, "leb_attention: head_dim %d outside 1..256", hd);
   LEB_REQUIRE(page_size % 32 == 0, "leb_attention: page size %d is not a multiple of 32", page_size);
   LEB_REQUIRE(n_splits >= 1 && (n_splits == 1 || (max_qlen == 1 && part)), "leb_attention: splits need single-row sequences and scratch");
   int rc;
 #define LEB_ATT(T, CT)                                                                            \
-  (hd <= 32    ? launch_attention<T, CT, 1>(out, part, q, k_pool, v_pool, block_table, bt_width,  \
+  (vd <= 32    ? launch_attention<T, CT, 1>(out, part, q, k_pool, v_pool, block_table, bt_width,  \
                                             seq_slot, seq_pos0, seq_qstart, seq_qlen, gate,       \
-                                            gate_stride, B, nh, nkv, hd, page_size, window,      \
+                                            gate_stride, B, nh, nkv, hd, vd, page_size, window,      \
                                             scale, max_qlen, n_splits, st)                        \
-   : hd <= 64  ? launch_attention<T, CT, 2>(out, part, q, k_pool, v_pool, block_table, bt_width,  \
+   : vd <= 64  ? launch_attention<T, CT, 2>(out, part, q, k_pool, v_pool, block_table, bt_width,  \
                                             seq_slot, seq_pos0, seq_qstart, seq_qlen, gate,       \
-                                            gate_stride, B, nh, nkv, hd, page_size, window,      \
+                                            gate_stride, B, nh, nkv, hd, vd, page_size, window,      \
                                             scale, max_qlen, n_splits, st)                        \
-   : hd <= 128 ? launch_attention<T, CT, 4>(out, part, q, k_pool, v_pool, block_table, bt_width,  \
+   : vd <= 128 ? launch_attention<T, CT, 4>(out, part, q, k_pool, v_pool, block_table, bt_width,  \
                                             seq_slot, seq_pos0, seq_qstart, seq_qlen, gate,       \
-                                            gate_stride, B, nh, nkv, hd, page_size, window,      \
+                                            gate_stride, B, nh, nkv, hd, vd, page_size, window,      \
                                             scale, max_qlen, n_splits, st)                        \
                : launch_attention<T, CT, 8>(out, part, q, k_pool, v_pool, block_table, bt_width,  \
                                             seq_slot, seq_pos0, seq_qstart, seq_qlen, gate,       \
-                                            gate_stride, B, nh, nkv, hd, page_size, window,      \
+                                            gate_stride, B, nh, nkv, hd, vd, page_size, window,      \
                                             scale, max_qlen, n_splits, st))
   if (dtype == LEB_F32)
     rc = LEB_ATT(float, float);
@@ -307,9 +311,9 @@ LEB_API int leb_attention(void* out, float* part, const void* q, const void* k_p
   if (n_splits > 1) {
     dim3 grid(M, nh);
     if (dtype == LEB_F32)
-      attention_merge_kernel<float><<<grid, 64, 0, st>>>((float*)out, part, (const float*)gate, gate_stride, nh, hd, n_splits);
+      attention_merge_kernel<float><<<grid, 64, 0, st>>>((float*)out, part, (const float*)gate, gate_stride, nh, vd, n_splits);
     else
-      attention_merge_kernel<bf16><<<grid, 64, 0, st>>>((bf16*)out, part, (const bf16*)gate, gate_stride, nh, hd, n_splits);
+      attention_merge_kernel<bf16><<<grid, 64, 0, st>>>((bf16*)out, part, (const bf16*)gate, gate_stride, nh, vd, n_splits);
     LEB_CHECK_LAUNCH("leb_attention merge");
   }
   return 0;

@@ -223,3 +223,93 @@ LEB_API int leb_add(float* x, const float* y, size_t n, cudaStream_t st) {
   LEB_CHECK_LAUNCH("leb_add");
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// a[m, j] = act(gu[m, j]) * gu[m, F + j] with act chosen by code: 0 silu, 1 the tanh form of gelu,
+// gelu(z) = z/2 * (1 + tanh(sqrt(2/pi) * (z + 0.044715 z^3))).
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+template <typename TI, typename TO>
+__global__ void gated_act_kernel(TO* __restrict__ a, const TI* __restrict__ gu, int F, size_t total, int act) {
+  pdl_trigger();
+  pdl_wait();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  size_t m = i / F;
+  int j = (int)(i - m * F);
+  float g = to_f32(gu[m * 2 * F + j]);
+  float u = to_f32(gu[m * 2 * F + F + j]);
+  float r = act == 1 ? gelu_tanh_f(g) * u : g / (1.0f + expf(-g)) * u;
+  a[i] = from_f32<TO>(r);
+}
+
+LEB_API int leb_gated_act(void* a, int out_dtype, const void* gu, int in_dtype, int M, int F, int act,
+                          cudaStream_t st) {
+  size_t total = (size_t)M * F;
+  if (total == 0) return 0;
+  LEB_REQUIRE(act == 0 || act == 1, "leb_gated_act: unknown activation %d", act);
+  dim3 grid((unsigned)((total + 255) / 256)), block(256);
+  if (in_dtype == LEB_F32 && out_dtype == LEB_F32)
+    leb_launch(gated_act_kernel<float, float>, grid, block, 0, st, (float*)a, (const float*)gu, F, total, act);
+  else if (in_dtype == LEB_F32 && out_dtype == LEB_BF16)
+    leb_launch(gated_act_kernel<float, bf16>, grid, block, 0, st, (bf16*)a, (const float*)gu, F, total, act);
+  else if (in_dtype == LEB_BF16 && out_dtype == LEB_BF16)
+    leb_launch(gated_act_kernel<bf16, bf16>, grid, block, 0, st, (bf16*)a, (const bf16*)gu, F, total, act);
+  else
+    return leb_fail("leb_gated_act: unsupported dtypes in=%d out=%d", in_dtype, out_dtype);
+  LEB_CHECK_LAUNCH("leb_gated_act");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// The gated residual: x[m, i] += y[m, i] * sigmoid(z[m, i] + b[i]); x, y and b are float, the gate's
+// pre-activation z comes from a matrix product in float or bfloat16.  Sum and sigmoid are float.
+template <typename TZ>
+__global__ void gated_residual_kernel(float* __restrict__ x, const float* __restrict__ y,
+                                      const TZ* __restrict__ z, const float* __restrict__ b, int D, size_t total) {
+  pdl_trigger();
+  pdl_wait();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  int c = (int)(i % D);
+  float zz = to_f32(z[i]) + (b ? b[c] : 0.f);
+  x[i] += y[i] * (1.0f / (1.0f + expf(-zz)));
+}
+
+LEB_API int leb_gated_residual(float* x, const float* y, const void* z, int z_dtype, const float* b, int M, int D,
+                               cudaStream_t st) {
+  size_t total = (size_t)M * D;
+  if (total == 0) return 0;
+  dim3 grid((unsigned)((total + 255) / 256)), block(256);
+  if (z_dtype == LEB_F32)
+    leb_launch(gated_residual_kernel<float>, grid, block, 0, st, x, y, (const float*)z, b, D, total);
+  else if (z_dtype == LEB_BF16)
+    leb_launch(gated_residual_kernel<bf16>, grid, block, 0, st, x, y, (const bf16*)z, b, D, total);
+  else
+    return leb_fail("leb_gated_residual: unknown dtype %d", z_dtype);
+  LEB_CHECK_LAUNCH("leb_gated_residual");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Additions to the residual stream between layers: x[m, :] += x0[m, :] (if given) + vec[:] (if given).
+__global__ void stream_add_kernel(float* __restrict__ x, const float* __restrict__ x0,
+                                  const float* __restrict__ vec, int D, size_t total) {
+  pdl_trigger();
+  pdl_wait();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  float v = x[i];
+  if (x0) v += x0[i];
+  if (vec) v += vec[i % D];
+  x[i] = v;
+}
+
+LEB_API int leb_stream_add(float* x, const float* x0, const float* vec, int M, int D, cudaStream_t st) {
+  size_t total = (size_t)M * D;
+  if (total == 0 || (!x0 && !vec)) return 0;
+  leb_launch(stream_add_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, x, x0, vec, D, total);
+  LEB_CHECK_LAUNCH("leb_stream_add");
+  return 0;
+}

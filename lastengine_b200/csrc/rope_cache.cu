@@ -29,10 +29,11 @@ __device__ __forceinline__ void store_value_tile(
     int t, const T* __restrict__ v_in, int kv_stride, CT* __restrict__ v_pool,
     const int* __restrict__ block_table, int bt_width, const int* __restrict__ row_seq,
     const int* __restrict__ row_pos, const int* __restrict__ seq_slot, int M, int nkv, int hd,
-    int page_size) {
+    int page_size, int v_norm, float eps) {
   constexpr int LD = VT_DIMS + (sizeof(CT) == 2 ? 2 : 1);     // odd number of 32-bit words
   __shared__ CT tile[VT_ROWS * LD];
   __shared__ long long dst[VT_ROWS];                          // element offset of (row, dim 0), or -1
+  __shared__ float rs[VT_ROWS];                               // 1 / root mean square of the row's head, or 1
   const int kvh = t % nkv, m0 = (t / nkv) * VT_ROWS;
   if (threadIdx.x < VT_ROWS) {
     int m = m0 + threadIdx.x;
@@ -46,13 +47,24 @@ __device__ __forceinline__ void store_value_tile(
     }
     dst[threadIdx.x] = off;
   }
+  // values divided by their root mean square over the head (no weight) where the layer asks for it
+  for (int r = threadIdx.x >> 5; r < VT_ROWS; r += blockDim.x >> 5) {
+    float ss = 0.f;
+    if (v_norm && m0 + r < M)
+      for (int d = threadIdx.x & 31; d < hd; d += 32) {
+        float x = to_f32(v_in[(size_t)(m0 + r) * kv_stride + (size_t)kvh * hd + d]);
+        ss += x * x;
+      }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) rs[r] = v_norm ? 1.0f / sqrtf(ss / (float)hd + eps) : 1.f;
+  }
   for (int d0 = 0; d0 < hd; d0 += VT_DIMS) {
     int nd = min(VT_DIMS, hd - d0);
     __syncthreads();
     for (int i = threadIdx.x; i < VT_ROWS * VT_DIMS; i += blockDim.x) {
       int r = i / VT_DIMS, d = i % VT_DIMS;
       if (d < nd && m0 + r < M)
-        tile[r * LD + d] = from_f32<CT>(to_f32(v_in[(size_t)(m0 + r) * kv_stride + (size_t)kvh * hd + d0 + d]));
+        tile[r * LD + d] = from_f32<CT>(to_f32(v_in[(size_t)(m0 + r) * kv_stride + (size_t)kvh * hd + d0 + d]) * rs[r]);
     }
     __syncthreads();
     for (int i = threadIdx.x; i < VT_ROWS * VT_DIMS; i += blockDim.x) {
@@ -73,7 +85,7 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_rope_store_kernel(
     const int* __restrict__ row_pos, const int* __restrict__ seq_slot,
     const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
     const float* __restrict__ inv_freq, int rope_dim, int neox, int M, int nh, int nkv, int hd,
-    int page_size) {
+    int page_size, int vd, int v_norm) {
   extern __shared__ float sm[];
   pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
@@ -81,7 +93,7 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_rope_store_kernel(
   if ((int)blockIdx.x >= M) {
     if (blockIdx.y == 0)
       store_value_tile<T, CT>(blockIdx.x - M, v_in, kv_stride, v_pool, block_table, bt_width, row_seq, row_pos,
-                              seq_slot, M, nkv, hd, page_size);
+                              seq_slot, M, nkv, vd, page_size, v_norm, eps);
     return;
   }
   // ---- one row: q and k heads ----
@@ -158,14 +170,14 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_rope_store_lanes_kernel(
     const int* __restrict__ block_table, int bt_width,
     const int* __restrict__ row_seq, const int* __restrict__ row_pos, const int* __restrict__ seq_slot,
     const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
-    const float* __restrict__ inv_freq, int M, int nh, int nkv, int page_size, int per_warp) {
+    const float* __restrict__ inv_freq, int M, int nh, int nkv, int page_size, int per_warp, int vd, int v_norm) {
   constexpr int HD = EPL * 32, NP = EPL / 2, U = 4;
   pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
   if ((int)blockIdx.x >= M) {
     if (blockIdx.y == 0)
       store_value_tile<T, CT>(blockIdx.x - M, v_in, kv_stride, v_pool, block_table, bt_width, row_seq, row_pos,
-                              seq_slot, M, nkv, HD, page_size);
+                              seq_slot, M, nkv, vd, page_size, v_norm, eps);
     return;
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -246,11 +258,12 @@ LEB_API int leb_qk_rope_store(void* q_out, const void* q_in, int q_stride, const
                               int dtype, const int* block_table, int bt_width, const int* row_seq,
                               const int* row_pos, const int* seq_slot, const float* q_norm_w,
                               const float* k_norm_w, float eps, const float* inv_freq, int rope_dim,
-                              int neox, int M, int nh, int nkv, int hd, int page_size,
+                              int neox, int M, int nh, int nkv, int hd, int page_size, int vd, int v_norm,
                               cudaStream_t st) {
   if (M <= 0) return 0;
   LEB_REQUIRE(hd >= 2 && hd <= 512, "leb_qk_rope_store: head_dim %d outside 2..512", hd);
   LEB_REQUIRE(rope_dim <= hd && rope_dim % 2 == 0, "leb_qk_rope_store: rope_dim %d does not fit head_dim %d", rope_dim, hd);
+  if (vd <= 0) vd = hd;      // values as wide as keys
   int tiles = k_in ? ceil_div(M, VT_ROWS) * nkv : 0;
   int total = nh + (k_in ? nkv : 0);
   dim3 block(32 * ROPE_WARPS);
@@ -264,12 +277,12 @@ LEB_API int leb_qk_rope_store(void* q_out, const void* q_in, int q_stride, const
       leb_launch(qk_rope_store_lanes_kernel<bf16, bf16, 2>, grid, block, 0, st,
           (bf16*)q_out, (const bf16*)q_in, q_stride, (const bf16*)k_in, (const bf16*)v_in, kv_stride,
           (bf16*)k_pool, (bf16*)v_pool, block_table, bt_width, row_seq, row_pos, seq_slot, q_norm_w,
-          k_norm_w, eps, inv_freq, M, nh, nkv, page_size, per_warp);
+          k_norm_w, eps, inv_freq, M, nh, nkv, page_size, per_warp, vd, v_norm);
     else
       leb_launch(qk_rope_store_lanes_kernel<bf16, bf16, 4>, grid, block, 0, st,
           (bf16*)q_out, (const bf16*)q_in, q_stride, (const bf16*)k_in, (const bf16*)v_in, kv_stride,
           (bf16*)k_pool, (bf16*)v_pool, block_table, bt_width, row_seq, row_pos, seq_slot, q_norm_w,
-          k_norm_w, eps, inv_freq, M, nh, nkv, page_size, per_warp);
+          k_norm_w, eps, inv_freq, M, nh, nkv, page_size, per_warp, vd, v_norm);
     LEB_CHECK_LAUNCH("leb_qk_rope_store");
     return 0;
   }
@@ -279,12 +292,12 @@ LEB_API int leb_qk_rope_store(void* q_out, const void* q_in, int q_stride, const
     leb_launch(qk_rope_store_kernel<float, float>, grid, block, smem, st,
         (float*)q_out, (const float*)q_in, q_stride, (const float*)k_in, (const float*)v_in,
         kv_stride, (float*)k_pool, (float*)v_pool, block_table, bt_width, row_seq, row_pos,
-        seq_slot, q_norm_w, k_norm_w, eps, inv_freq, rope_dim, neox, M, nh, nkv, hd, page_size);
+        seq_slot, q_norm_w, k_norm_w, eps, inv_freq, rope_dim, neox, M, nh, nkv, hd, page_size, vd, v_norm);
   else if (dtype == LEB_BF16)
     leb_launch(qk_rope_store_kernel<bf16, bf16>, grid, block, smem, st,
         (bf16*)q_out, (const bf16*)q_in, q_stride, (const bf16*)k_in, (const bf16*)v_in, kv_stride,
         (bf16*)k_pool, (bf16*)v_pool, block_table, bt_width, row_seq, row_pos, seq_slot, q_norm_w,
-        k_norm_w, eps, inv_freq, rope_dim, neox, M, nh, nkv, hd, page_size);
+        k_norm_w, eps, inv_freq, rope_dim, neox, M, nh, nkv, hd, page_size, vd, v_norm);
   else
     return leb_fail("leb_qk_rope_store: unknown dtype %d", dtype);
   LEB_CHECK_LAUNCH("leb_qk_rope_store");

@@ -295,7 +295,10 @@ class Engine:
             blk = self.model.blocks[e.layer]
             layer_flops += sum(p.flops_per_row() for p in blk.parts().values())
             pair_flops += blk.mixer.flops_per_query_key()
+        specs = []
         for spec in self.model.cache_specs().values():
+            specs += list(spec) if isinstance(spec, (tuple, list)) else [spec]
+        for spec in specs:
             if spec is None:
                 continue
             if hasattr(spec, "n_kv_heads"):

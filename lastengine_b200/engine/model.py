@@ -10,7 +10,9 @@ import torch
 
 from .. import parts as _parts  # noqa: F401  (registers the built-in parts)
 from ..parts.base import BuildEnv, ModelPlan, TensorSpec
-from ..registry import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS
+from ..ops import kernels
+from ..parts.base import VECTOR
+from ..registry import BLOCKS, EMBEDDINGS, FEED_FORWARDS, GATES, HEADS, MIXERS, NORMS
 
 
 class Model:
@@ -22,12 +24,19 @@ class Model:
         self.blocks = []
         for ls in plan.layers:
             mixer = MIXERS.get(ls.mixer.kind)(**ls.mixer.params)
-            ffn = FEED_FORWARDS.get(ls.ffn.kind)(**ls.ffn.params)
+            ffn = None if ls.ffn is None else FEED_FORWARDS.get(ls.ffn.kind)(**ls.ffn.params)
             norm = lambda s: None if s is None else NORMS.get(s.kind)(**s.params)  # noqa: E731
+            gates = {role: GATES.get(g.kind)(**g.params) for role, g in ls.gates.items()}
             self.blocks.append(BLOCKS.get(ls.block)(
                 mixer=mixer, ffn=ffn, mixer_norm=norm(ls.mixer_norm), ffn_norm=norm(ls.ffn_norm),
-                post_mixer_norm=norm(ls.post_mixer_norm), post_ffn_norm=norm(ls.post_ffn_norm)))
+                post_mixer_norm=norm(ls.post_mixer_norm), post_ffn_norm=norm(ls.post_ffn_norm), **gates))
         self.hidden_size, self.vocab_size = plan.hidden_size, plan.vocab_size
+        # additions to the residual stream between schedule entries, and the tables they take rows from
+        self.stream_adds: dict[int, list] = {}
+        for a in plan.stream_adds:
+            self.stream_adds.setdefault(a.before, []).append(a)
+        self.keeps_embedding = any(a.embedding for a in plan.stream_adds)
+        self.stream_tables: dict[str, torch.Tensor] = {}
 
     # ---- tensors ------------------------------------------------------------------------
     def named_parts(self) -> list[tuple[str, object]]:
@@ -41,14 +50,21 @@ class Model:
                 out.append((f"{ls.prefix}.{ls.names.get(role, role)}", part))
         return out
 
+    @staticmethod
+    def _name(prefix: str, rel: str, spec: TensorSpec) -> str:
+        """A part's tensor under its prefix; the relative name "" is the prefix itself."""
+        return spec.shared_name or (f"{prefix}.{rel}" if rel else prefix)
+
     def tensor_specs(self) -> dict[str, TensorSpec]:
         specs: dict[str, TensorSpec] = {}
         for prefix, part in self.named_parts():
             for rel, spec in part.tensors().items():
-                name = spec.shared_name or f"{prefix}.{rel}"
+                name = self._name(prefix, rel, spec)
                 if name in specs and specs[name] != spec:
                     raise ValueError(f"tensor '{name}' is declared twice, as {specs[name]} and as {spec}")
                 specs[name] = spec
+        for name, shape in self.plan.stream_tables.items():
+            specs[name] = TensorSpec(tuple(shape), VECTOR)
         return specs
 
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
@@ -56,10 +72,11 @@ class Model:
         for prefix, part in self.named_parts():
             own = {}
             for rel, spec in part.tensors().items():
-                name = spec.shared_name or f"{prefix}.{rel}"
+                name = self._name(prefix, rel, spec)
                 if name in tensors:
                     own[rel] = tensors[name]
             part.load(own, self.env)
+        self.stream_tables = {n: tensors[n].contiguous() for n in self.plan.stream_tables if n in tensors}
         if getattr(self.head, "tied", False):
             self.head.tie(self.embedding)
 
@@ -79,12 +96,20 @@ class Model:
         M, D = batch.n_rows, self.hidden_size
         x = ws.get("model.x", (M, D), torch.float32)
         self.embedding.forward(x, batch.tokens)
+        x0 = None
+        if self.keeps_embedding:      # the embedding output is added to the stream again later
+            x0 = ws.get("model.x0", (M, D), torch.float32)
+            self.embedding.forward(x0, batch.tokens)
         sched = self.plan.schedule
         pending = None      # the half of the next block's first norm that the last block left (decode steps)
         for i, e in enumerate(sched):
             entry = i if e.cache is None else e.cache
             view = cache.view(entry, e.writes_cache and entry == i, batch.tables)
             block = self.blocks[e.layer]
+            for a in self.stream_adds.get(i, ()):
+                kernels.stream_add(x, x0 if a.embedding else None,
+                                   self.stream_tables[a.table][a.row] if a.table is not None else None)
+                pending = None      # a norm half left for this block was taken from the stream as it was before
             after = self.blocks[sched[i + 1].layer] if i + 1 < len(sched) else None
             # (norm, part that reads it) of the block that runs next, for blocks that can split a norm
             env.next_block_norm = after.first_reader() if hasattr(after, "first_reader") else None

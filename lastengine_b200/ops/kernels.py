@@ -98,8 +98,13 @@ def _declare(L) -> None:
         "leb_gather_rows": [P, P, I, P, I, I, I, P],
         "leb_add": [P, P, S, P],
         "leb_shortconv": [P, P, I, P, P, P, P, P, P, P, I, I, I, I, P],
-        "leb_qk_rope_store": [P, P, I, P, P, I, P, P, I, P, I, P, P, P, P, P, F, P, I, I, I, I, I, I, I, P],
-        "leb_attention": [P, P, P, P, P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P],
+        "leb_qk_rope_store": [P, P, I, P, P, I, P, P, I, P, I, P, P, P, P, P, F, P, I, I, I, I, I, I, I, I, I, P],
+        "leb_attention": [P, P, P, P, P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, I, P],
+        "leb_gated_act": [P, I, P, I, I, I, I, P],
+        "leb_gated_residual": [P, P, P, I, P, I, I, P],
+        "leb_stream_add": [P, P, P, I, I, P],
+        "leb_causal_conv": [P, I, P, I, I, P, P, P, P, P, P, I, I, I, I, I, P],
+        "leb_retention": [P, P, P, P, P, I, I, P, P, P, I, F, F, P, P, P, P, I, I, I, I, I, P],
         "leb_gemm_f32": [P, P, P, I, I, I, I, I, I, P, I, S, P],
         "leb_gemm_bf16_small": [P, I, P, P, I, I, I, I, I, I, P, I, S, I, P],
         "leb_gemm_bf16_stream": [P, I, P, P, I, I, I, I, I, I, P, I, I, F, P, P, P, P],
@@ -233,6 +238,93 @@ def swiglu(out: torch.Tensor, gu: torch.Tensor) -> None:
     _check(lib().leb_swiglu(_ptr(out), _dt(out, "swiglu.out"), _ptr(gu), _dt(gu, "swiglu.gu"), M, Fd, _stream()))
 
 
+SILU, GELU_TANH = 0, 1      # activations of a gated feed-forward
+
+
+def gated_act(out: torch.Tensor, gu: torch.Tensor, act: int) -> None:
+    """out[m, j] = act(gu[m, j]) * gu[m, F + j], act SILU or GELU_TANH."""
+    _cuda(out, "gated_act.out")
+    _cuda(gu, "gated_act.gu")
+    M, Fd = out.shape
+    assert gu.shape == (M, 2 * Fd)
+    _check(lib().leb_gated_act(_ptr(out), _dt(out, "gated_act.out"), _ptr(gu), _dt(gu, "gated_act.gu"), M, Fd,
+                               int(act), _stream()))
+
+
+def gated_residual(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor, bias: torch.Tensor | None) -> None:
+    """x += y * sigmoid(z + bias): x and y float [M, D], z the gate's pre-activation [M, D], bias float [D]."""
+    _cuda(x, "gated_residual.x", torch.float32)
+    _cuda(y, "gated_residual.y", torch.float32)
+    _cuda(z, "gated_residual.z")
+    M, D = x.shape
+    assert y.shape == (M, D) and z.shape == (M, D)
+    if bias is not None:
+        _cuda(bias, "gated_residual.bias", torch.float32)
+        assert bias.numel() == D
+    _check(lib().leb_gated_residual(_ptr(x), _ptr(y), _ptr(z), _dt(z, "gated_residual.z"), _ptr(bias), M, D, _stream()))
+
+
+def stream_add(x: torch.Tensor, x0: torch.Tensor | None, vec: torch.Tensor | None) -> None:
+    """x[m] += x0[m] (if given) + vec (if given); all float."""
+    _cuda(x, "stream_add.x", torch.float32)
+    M, D = x.shape
+    if x0 is not None:
+        _cuda(x0, "stream_add.x0", torch.float32)
+        assert x0.shape == (M, D)
+    if vec is not None:
+        _cuda(vec, "stream_add.vec", torch.float32)
+        assert vec.numel() == D
+    _check(lib().leb_stream_add(_ptr(x), _ptr(x0), _ptr(vec), M, D, _stream()))
+
+
+def causal_conv(y: torch.Tensor, u: torch.Tensor, w: torch.Tensor, state: torch.Tensor, batch) -> None:
+    """Causal depthwise convolution over time on every column of u [M, C] (a column slice is fine),
+    taps [C, taps] float, with `state` [slots, C, taps-1] float holding each sequence's last
+    projected values; writes y [M, C] and moves the state on."""
+    _cuda(y, "causal_conv.y", contiguous=False)
+    _cuda(u, "causal_conv.u", y.dtype, contiguous=False)
+    _cuda(w, "causal_conv.w", torch.float32)
+    M, C = y.shape
+    taps = w.shape[1]
+    assert u.shape == (M, C) and w.shape == (C, taps) and u.stride(1) == 1 and y.stride(1) == 1
+    if taps > 1:
+        _cuda(state, "causal_conv.state", torch.float32)
+        assert state.shape[1:] == (C, taps - 1)
+    else:
+        state = None      # a single tap keeps nothing
+    single = batch.max_qlen == 1 and M == batch.n_seqs
+    _check(lib().leb_causal_conv(_ptr(y), y.stride(0), _ptr(u), u.stride(0), _dt(y, "causal_conv"), _ptr(w), _ptr(state),
+                                 _ptr(batch.row_seq), _ptr(batch.seq_slot), _ptr(batch.seq_qstart), _ptr(batch.seq_qlen),
+                                 M, batch.n_seqs, C, taps, 1 if single else 0, _stream()))
+
+
+def retention(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
+              state: torch.Tensor, decay: torch.Tensor, inv_freq: torch.Tensor | None, rot: int, k_scale: float,
+              eps: float, batch, H: int, d: int, e: int) -> None:
+    """Decayed linear attention of the step's rows with the per-sequence state [slots, H, d, e] (float):
+    q and k rotated on their first `rot` dimensions, k scaled, S = decay S + k v^T, o = S^T q,
+    o divided by its root mean square per head and multiplied by silu(g).  q, k [M, H*d] and v, g
+    [M, H*e] are column slices of one projection."""
+    _cuda(out, "retention.out")
+    M = out.shape[0]
+    assert out.shape == (M, H * e)
+    ld = q.stride(0)
+    for n, t, w in (("q", q, H * d), ("k", k, H * d), ("v", v, H * e), ("g", g, H * e)):
+        _cuda(t, f"retention.{n}", out.dtype, contiguous=False)
+        assert t.shape == (M, w) and t.stride(1) == 1 and t.stride(0) == ld
+    _cuda(state, "retention.state", torch.float32)
+    _cuda(decay, "retention.decay", torch.float32)
+    assert state.shape[1:] == (H, d, e) and decay.numel() == H
+    if rot:
+        _cuda(inv_freq, "retention.inv_freq", torch.float32)
+        assert inv_freq.numel() == rot // 2
+    single = batch.max_qlen == 1 and M == batch.n_seqs
+    _check(lib().leb_retention(_ptr(out), _ptr(q), _ptr(k), _ptr(v), _ptr(g), ld, _dt(out, "retention"), _ptr(state),
+                               _ptr(decay), _ptr(inv_freq), int(rot), float(k_scale), float(eps), _ptr(batch.seq_slot),
+                               _ptr(batch.seq_pos0), _ptr(batch.seq_qstart), None if single else _ptr(batch.seq_qlen),
+                               M, batch.n_seqs, H, d, e, _stream()))
+
+
 def gather_rows(out: torch.Tensor, src: torch.Tensor, rows: torch.Tensor, div: int = 1) -> None:
     """out[p] = src[rows[p] // div]."""
     _cuda(out, "gather_rows.out")
@@ -321,11 +413,14 @@ def qk_rope_store(q_out: torch.Tensor, q_in: torch.Tensor, k_in: torch.Tensor | 
                   v_in: torch.Tensor | None, k_pool: torch.Tensor | None, v_pool: torch.Tensor | None,
                   block_table: torch.Tensor, batch, q_norm_w, k_norm_w, eps: float,
                   inv_freq: torch.Tensor | None, rope_dim: int, neox: bool, nh: int, nkv: int, hd: int,
-                  page_size: int) -> None:
+                  page_size: int, vd: int | None = None, v_norm: bool = False) -> None:
     """Per-head norm and rotation of q and k; k and v go to the paged cache, q to q_out.
 
     q_in/k_in/v_in may be column slices of one fused projection (row stride = its width).
+    `vd`: width of a value head where it is not the key head's; `v_norm`: every value head is
+    divided by its root mean square (with `eps`, no weight) before it is stored.
     """
+    vd = hd if vd is None else int(vd)
     _cuda(q_out, "qk_rope_store.q_out")
     _cuda(q_in, "qk_rope_store.q_in", q_out.dtype, contiguous=False)
     M = q_out.shape[0]
@@ -335,12 +430,12 @@ def qk_rope_store(q_out: torch.Tensor, q_in: torch.Tensor, k_in: torch.Tensor | 
     if k_in is not None:
         _cuda(k_in, "qk_rope_store.k_in", q_out.dtype, contiguous=False)
         _cuda(v_in, "qk_rope_store.v_in", q_out.dtype, contiguous=False)
-        assert k_in.shape == (M, nkv * hd) and v_in.shape == (M, nkv * hd)
+        assert k_in.shape == (M, nkv * hd) and v_in.shape == (M, nkv * vd)
         assert k_in.stride(0) == v_in.stride(0) and k_in.stride(-1) == 1 and v_in.stride(-1) == 1
         kv_stride = k_in.stride(0)
         _cuda(k_pool, "qk_rope_store.k_pool", q_out.dtype)
         _cuda(v_pool, "qk_rope_store.v_pool", q_out.dtype)
-        assert k_pool.shape[1:] == (nkv, page_size, hd) and v_pool.shape[1:] == (nkv, hd, page_size)
+        assert k_pool.shape[1:] == (nkv, page_size, hd) and v_pool.shape[1:] == (nkv, vd, page_size)
     _cuda(block_table, "qk_rope_store.block_table", torch.int32)
     for name, t in (("q_norm_w", q_norm_w), ("k_norm_w", k_norm_w), ("inv_freq", inv_freq)):
         if t is not None:
@@ -351,7 +446,7 @@ def qk_rope_store(q_out: torch.Tensor, q_in: torch.Tensor, k_in: torch.Tensor | 
         _ptr(q_out), _ptr(q_in), q_stride, _ptr(k_in), _ptr(v_in), kv_stride, _ptr(k_pool), _ptr(v_pool),
         _dt(q_out, "qk_rope_store"), _ptr(block_table), block_table.shape[1], _ptr(batch.row_seq),
         _ptr(batch.row_pos), _ptr(batch.seq_slot), _ptr(q_norm_w), _ptr(k_norm_w), float(eps),
-        _ptr(inv_freq), rope_dim, 1 if neox else 0, M, nh, nkv, hd, page_size, _stream()))
+        _ptr(inv_freq), rope_dim, 1 if neox else 0, M, nh, nkv, hd, page_size, vd, 1 if v_norm else 0, _stream()))
 
 
 _sm_counts: dict[int, int] = {}
@@ -417,10 +512,15 @@ def decode_attention_takes_raw(dtype: torch.dtype, batch, M: int, nh: int, nkv: 
 def attention(out: torch.Tensor, q: torch.Tensor | None, k_pool: torch.Tensor, v_pool: torch.Tensor,
               block_table: torch.Tensor, batch, nh: int, nkv: int, hd: int, page_size: int,
               window: int, scale: float, gate: torch.Tensor | None = None,
-              n_splits: int = 1, scratch: torch.Tensor | None = None, raw: RawQKV | None = None) -> None:
+              n_splits: int = 1, scratch: torch.Tensor | None = None, raw: RawQKV | None = None,
+              vd: int | None = None) -> None:
     """Causal attention of the step's rows over the paged cache (which already holds their keys;
-    with `raw`, the kernel puts the step's keys and values there itself and `q` is not used)."""
+    with `raw`, the kernel puts the step's keys and values there itself and `q` is not used).
+    `vd`: width of a value head where it differs from the key head's (the general kernel then)."""
     _cuda(out, "attention.out")
+    if vd is not None and vd != hd:
+        return _attention_general(out, q, k_pool, v_pool, block_table, batch, nh, nkv, hd, int(vd), page_size, window,
+                                  scale, gate, n_splits, scratch)
     if raw is not None:
         return _attention_decode_raw(out, raw, k_pool, v_pool, block_table, batch, nh, nkv, hd, page_size, window,
                                      scale, gate, n_splits, scratch)
@@ -476,7 +576,33 @@ def attention(out: torch.Tensor, q: torch.Tensor | None, k_pool: torch.Tensor, v
         _ptr(out), _ptr(scratch), _ptr(q), _ptr(k_pool), _ptr(v_pool), _dt(out, "attention"),
         _ptr(block_table), block_table.shape[1], _ptr(batch.seq_slot), _ptr(batch.seq_pos0),
         _ptr(batch.seq_qstart), _ptr(batch.seq_qlen), _ptr(gate), gate_stride, M, batch.n_seqs, nh, nkv,
-        hd, page_size, window, float(scale), batch.max_qlen, n_splits, _stream()))
+        hd, page_size, window, float(scale), batch.max_qlen, n_splits, hd, _stream()))
+
+
+def _attention_general(out, q, k_pool, v_pool, block_table, batch, nh, nkv, hd, vd, page_size, window, scale, gate,
+                       n_splits, scratch) -> None:
+    """The general kernel with value heads of their own width."""
+    _cuda(q, "attention.q", out.dtype)
+    _cuda(k_pool, "attention.k_pool", out.dtype)
+    _cuda(v_pool, "attention.v_pool", out.dtype)
+    _cuda(block_table, "attention.block_table", torch.int32)
+    M = out.shape[0]
+    assert out.shape == (M, nh * vd) and q.shape == (M, nh * hd)
+    assert k_pool.shape[1:] == (nkv, page_size, hd) and v_pool.shape[1:] == (nkv, vd, page_size)
+    gate_stride = 0
+    if gate is not None:
+        _cuda(gate, "attention.gate", out.dtype, contiguous=False)
+        assert gate.shape == (M, nh) and gate.stride(-1) == 1
+        gate_stride = gate.stride(0)
+    if n_splits > 1:
+        need = M * nh * n_splits * (vd + 2)
+        if scratch is None or scratch.numel() < need or scratch.dtype != torch.float32:
+            raise KernelError(f"attention: {n_splits} splits need {need} floats of scratch")
+    _check(lib().leb_attention(
+        _ptr(out), _ptr(scratch), _ptr(q), _ptr(k_pool), _ptr(v_pool), _dt(out, "attention"),
+        _ptr(block_table), block_table.shape[1], _ptr(batch.seq_slot), _ptr(batch.seq_pos0),
+        _ptr(batch.seq_qstart), _ptr(batch.seq_qlen), _ptr(gate), gate_stride, M, batch.n_seqs, nh, nkv,
+        hd, page_size, window, float(scale), batch.max_qlen, n_splits, vd, _stream()))
 
 
 def _attention_decode_raw(out, raw: RawQKV, k_pool, v_pool, block_table, batch, nh, nkv, hd, page_size, window,

@@ -6,6 +6,15 @@ causal softmax attention with scale 1/sqrt(head_dim), optionally inside a window
 sigmoid gate per head from its own projection; out = Wo o.  (src/dense.rs:113-152.)
 The three projections (and the gate) are one matrix product over fused weights, as the
 reference fuses gate and up (src/gpu/dense.rs:67-74).
+
+Options other designs use: value heads of a width of their own (`v_head_dim`); a short causal
+depthwise convolution over time on every channel of q, k and v right after the projection
+(`conv_taps` > 1; taps `<tensor>.conv` [channels, taps]; the last taps-1 projected values of a
+sequence are state beside its keys and values); q and k divided by their root mean square without
+a weight (`qk_norm="unit"`); every value head divided by its root mean square before it is cached
+(`v_norm`).  The kernels norm before they rotate; a design that rotates first gets the same
+numbers, since a rotation of pairs leaves the head's sum of squares as it was.  `names` renames
+the tensors under the part's prefix.
 """
 from __future__ import annotations
 
@@ -15,7 +24,7 @@ import torch
 
 from ..ops import kernels
 from ..registry import MIXERS, POSITION_ENCODINGS
-from .base import MATRIX, NORM, BuildEnv, KVSpec, Mixer, PartSpec, TensorSpec
+from .base import MATRIX, NORM, VECTOR, BuildEnv, KVSpec, Mixer, PartSpec, StateSpec, TensorSpec
 
 
 @MIXERS.register("attention")
@@ -25,14 +34,29 @@ class AttentionMixer(Mixer):
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  norm_eps: float, qk_norm: bool = True, position: PartSpec | None = None,
                  window: int = 0, output_gate: bool = False, own_kv: bool = True,
-                 scale: float | None = None):
+                 scale: float | None = None, v_head_dim: int | None = None, conv_taps: int = 0,
+                 v_norm: bool = False, names: dict[str, str] | None = None):
         if num_heads % num_kv_heads != 0:
             raise ValueError(f"{num_heads} heads do not divide into {num_kv_heads} kv heads")
         if head_dim > 256:
             raise ValueError(f"head_dim {head_dim} is larger than the attention kernels take (256)")
         self.D, self.nh, self.nkv, self.hd = int(hidden_size), int(num_heads), int(num_kv_heads), int(head_dim)
         self.eps = float(norm_eps)
-        self.qk_norm = bool(qk_norm)
+        self.qk_unit = qk_norm == "unit"            # divided by the root mean square, no weight
+        self.qk_norm = bool(qk_norm) and not self.qk_unit
+        self.vd = self.hd if v_head_dim is None else int(v_head_dim)
+        if self.vd > 256:
+            raise ValueError(f"v_head_dim {self.vd} is larger than the attention kernels take (256)")
+        self.taps = int(conv_taps)
+        if not 0 <= self.taps <= 16:
+            raise ValueError(f"conv_taps {conv_taps}: 0 (no convolution) or 1..16")
+        if self.taps and not own_kv:
+            raise ValueError("a layer that reads another layer's cache cannot convolve its own k and v")
+        self.v_norm = bool(v_norm)
+        self.n = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "out_proj.weight",
+                  "gate": "gate_proj.weight", "q_norm": "q_layernorm.weight", "k_norm": "k_layernorm.weight",
+                  "q_conv": "q_conv.weight", "k_conv": "k_conv.weight", "v_conv": "v_conv.weight"}
+        self.n.update(names or {})
         self.window = int(window)
         self.output_gate = bool(output_gate)
         self.own_kv = bool(own_kv)
@@ -42,46 +66,62 @@ class AttentionMixer(Mixer):
         self.w_in = self.w_out = self.q_norm_w = self.k_norm_w = None
 
     def tensors(self) -> dict[str, TensorSpec]:
-        D, nh, nkv, hd = self.D, self.nh, self.nkv, self.hd
-        t = {"q_proj.weight": TensorSpec((nh * hd, D), MATRIX),
-             "out_proj.weight": TensorSpec((D, nh * hd), MATRIX)}
+        D, nh, nkv, hd, vd, n = self.D, self.nh, self.nkv, self.hd, self.vd, self.n
+        t = {n["q"]: TensorSpec((nh * hd, D), MATRIX),
+             n["o"]: TensorSpec((D, nh * vd), MATRIX)}
         if self.own_kv:
-            t["k_proj.weight"] = TensorSpec((nkv * hd, D), MATRIX)
-            t["v_proj.weight"] = TensorSpec((nkv * hd, D), MATRIX)
+            t[n["k"]] = TensorSpec((nkv * hd, D), MATRIX)
+            t[n["v"]] = TensorSpec((nkv * vd, D), MATRIX)
         if self.qk_norm:
-            t["q_layernorm.weight"] = TensorSpec((hd,), NORM)
+            t[n["q_norm"]] = TensorSpec((hd,), NORM)
             if self.own_kv:
-                t["k_layernorm.weight"] = TensorSpec((hd,), NORM)
+                t[n["k_norm"]] = TensorSpec((hd,), NORM)
         if self.output_gate:
-            t["gate_proj.weight"] = TensorSpec((nh, D), MATRIX)
+            t[n["gate"]] = TensorSpec((nh, D), MATRIX)
+        if self.taps:
+            t[n["q_conv"]] = TensorSpec((nh * hd, self.taps), VECTOR, std=0.5)
+            t[n["k_conv"]] = TensorSpec((nkv * hd, self.taps), VECTOR, std=0.5)
+            t[n["v_conv"]] = TensorSpec((nkv * vd, self.taps), VECTOR, std=0.5)
         for name, spec in self.position.tensors().items():
             t[f"position.{name}"] = spec
         return t
 
     def cache_spec(self):
-        return KVSpec(self.nkv, self.hd, self.window)
+        kv = KVSpec(self.nkv, self.hd, self.window, None if self.vd == self.hd else self.vd)
+        if self.taps <= 1:       # a single tap looks at the current row only
+            return kv
+        # the convolution's memory: the last taps-1 projected values of every q, k and v channel
+        return kv, StateSpec(((self.nh + self.nkv) * self.hd + self.nkv * self.vd, self.taps - 1), torch.float32)
 
     def load(self, tensors, env: BuildEnv) -> None:
-        parts = [tensors["q_proj.weight"]]
+        n = self.n
+        parts = [tensors[n["q"]]]
         if self.own_kv:
-            parts += [tensors["k_proj.weight"], tensors["v_proj.weight"]]
+            parts += [tensors[n["k"]], tensors[n["v"]]]
         if self.output_gate:
-            parts.append(tensors["gate_proj.weight"])
+            parts.append(tensors[n["gate"]])
         self.w_in = torch.cat(parts, dim=0).contiguous() if len(parts) > 1 else parts[0].contiguous()
-        self.w_out = tensors["out_proj.weight"].contiguous()
+        self.w_out = tensors[n["o"]].contiguous()
         if self.qk_norm:
-            self.q_norm_w = tensors["q_layernorm.weight"].contiguous()
-            self.k_norm_w = tensors["k_layernorm.weight"].contiguous() if self.own_kv else None
+            self.q_norm_w = tensors[n["q_norm"]].contiguous()
+            self.k_norm_w = tensors[n["k_norm"]].contiguous() if self.own_kv else None
+        elif self.qk_unit:
+            self.q_norm_w = self.k_norm_w = torch.ones(self.hd, dtype=torch.float32, device=env.device)
+        self.w_conv = None
+        if self.taps:
+            self.w_conv = torch.cat([tensors[n["q_conv"]], tensors[n["k_conv"]], tensors[n["v_conv"]]],
+                                    dim=0).to(torch.float32).contiguous()
         self.position.load({n[len("position."):]: v for n, v in tensors.items() if n.startswith("position.")}, env)
 
     def split_reader_weight(self):
         return self.w_in
 
     def flops_per_query_key(self) -> int:
-        return 4 * self.nh * self.hd        # a score and a weighted value, a multiply-add each, per head and dimension
+        return 2 * self.nh * (self.hd + self.vd)    # a score and a weighted value, a multiply-add each, per head and dimension
 
     def forward(self, h, out, accumulate, batch, cache, env) -> None:
-        nh, nkv, hd = self.nh, self.nkv, self.hd
+        nh, nkv, hd, vd = self.nh, self.nkv, self.hd, self.vd
+        plain_v = vd == hd and not self.v_norm
         M = h.shape[0]
         ws = env.workspace
         scale, emit = env.take_split_in(), env.take_split_out()
@@ -99,21 +139,33 @@ class AttentionMixer(Mixer):
         col = nh * hd
         if writes:
             k_in = proj[:, col: col + nkv * hd]
-            v_in = proj[:, col + nkv * hd: col + 2 * nkv * hd]
-            col += 2 * nkv * hd
+            v_in = proj[:, col + nkv * hd: col + nkv * (hd + vd)]
+            col += nkv * (hd + vd)
         if self.output_gate:
             gate = proj[:, col: col + nh]
+        if self.taps:
+            # q, k and v (not the gate) through the short convolution; the state moves on by the step's rows
+            if not writes:
+                raise NotImplementedError("a convolved attention layer that does not write its cache")
+            conv = ws.get("attn.conv", (M, col), env.dtype)
+            kernels.causal_conv(conv, proj[:, :col], self.w_conv, cache.state, batch)
+            q_in, k_in = conv[:, : nh * hd], conv[:, nh * hd: (nh + nkv) * hd]
+            v_in = conv[:, (nh + nkv) * hd:]
         q = ws.get("attn.q", (M, nh * hd), env.dtype)
         kp, vp = (cache.k, cache.v) if writes else (None, None)
         rotary = self.position.fused_rotary()
         raw = None
-        if rotary is not None and kernels.decode_attention_takes_raw(env.dtype, batch, M, nh, nkv, hd, cache.page_size, *rotary):
+        if (rotary is not None and plain_v
+                and kernels.decode_attention_takes_raw(env.dtype, batch, M, nh, nkv, hd, cache.page_size, *rotary)):
             # a decode step: the attention kernel norms and rotates q and k and stores k and v itself
             raw = kernels.RawQKV(q_in, k_in, v_in, self.q_norm_w, self.k_norm_w if writes else None, self.eps, *rotary)
         elif rotary is not None:
             # per-head norm, rotation and the cache write in one launch
             kernels.qk_rope_store(q, q_in, k_in, v_in, kp, vp, cache.block_table, batch, self.q_norm_w,
-                                  self.k_norm_w if writes else None, self.eps, *rotary, nh, nkv, hd, cache.page_size)
+                                  self.k_norm_w if writes else None, self.eps, *rotary, nh, nkv, hd, cache.page_size,
+                                  vd=vd, v_norm=self.v_norm)
+        elif not plain_v:
+            raise NotImplementedError("value heads of their own width or norm with a position encoding that is no rotation")
         else:
             # an encoding of the part's own: norm, then the part on the normed q and k, then the store
             qn = ws.get("attn.qn", (M, nh * hd), env.dtype)
@@ -130,12 +182,13 @@ class AttentionMixer(Mixer):
             self.position.apply(qn.view(M, nh, hd), kn.view(M, nkv, hd) if writes else None, batch.row_pos)
             kernels.qk_rope_store(q, qn, kn, vn, kp, vp, cache.block_table, batch, None, None, self.eps,
                                   None, 0, True, nh, nkv, hd, cache.page_size)
-        o = ws.get("attn.o", (M, nh * hd), env.dtype)
+        o = ws.get("attn.o", (M, nh * vd), env.dtype)
         n_splits = kernels.attention_splits(batch, nkv, nh // nkv, hd=hd)
         scratch = None
         if n_splits > 1:
-            scratch = ws.get("attn.part", (M * nh * n_splits * (hd + 2),), torch.float32)
+            scratch = ws.get("attn.part", (M * nh * n_splits * (max(hd, vd) + 2),), torch.float32)
         kernels.attention(o, None if raw is not None else q, cache.k, cache.v, cache.block_table, batch, nh, nkv, hd,
-                          cache.page_size, self.window, self.scale, gate=gate, n_splits=n_splits, scratch=scratch, raw=raw)
+                          cache.page_size, self.window, self.scale, gate=gate, n_splits=n_splits, scratch=scratch, raw=raw,
+                          vd=vd)
         kernels.linear(out, o, self.w_out, kernels.ACCUMULATE if accumulate else kernels.STORE,
                        emit=emit if accumulate else None)

@@ -13,7 +13,8 @@ Every part:
     load(tensors, env)                             takes its tensors (already on the device,
                                                    in the dtype of their role) and may fuse them
 Mixer:
-    cache_spec() -> KVSpec | StateSpec | None      what it keeps per sequence
+    cache_spec() -> KVSpec | StateSpec | None      what it keeps per sequence (or a tuple of one
+                    | (KVSpec, StateSpec)           KVSpec and one StateSpec for a mixer that keeps both)
     forward(h, out, accumulate, batch, cache, env) h: [rows, hidden] normed input in the
                                                    activation dtype; writes (or adds) its
                                                    result into the float tensor `out`
@@ -38,10 +39,11 @@ import torch
 MATRIX = "matrix"        # operand of a matrix product: kept in the compute dtype
 EMBEDDING = "embedding"  # token table: compute dtype
 NORM = "norm"            # norm weight: kept float
+NORM_AROUND_ZERO = "norm0"   # norm weight stored around zero (the factor is 1 + w): kept float
 VECTOR = "vector"        # small per-channel parameters (conv taps, router rows): kept float
 BIAS = "bias"            # additive terms: kept float
 
-FLOAT_ROLES = (NORM, VECTOR, BIAS)
+FLOAT_ROLES = (NORM, NORM_AROUND_ZERO, VECTOR, BIAS)
 
 
 @dataclass(frozen=True)
@@ -85,14 +87,26 @@ class PartSpec:
 class LayerSpec:
     prefix: str                    # tensor-name prefix of the layer, e.g. "layers.3"
     mixer: PartSpec
-    ffn: PartSpec
+    ffn: PartSpec | None           # None: the layer has no feed-forward sublayer (a block arrangement that allows it)
     mixer_norm: PartSpec
-    ffn_norm: PartSpec
+    ffn_norm: PartSpec | None
     post_mixer_norm: PartSpec | None = None
     post_ffn_norm: PartSpec | None = None
     block: str = "pre_norm_residual"
     # tensor-name prefixes of the parts, relative to `prefix`
     names: dict[str, str] = field(default_factory=dict)
+    # gates on the sublayers' results, by the name under which the block arrangement takes them
+    gates: dict[str, PartSpec] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class StreamAdd:
+    """Something added to the residual stream right before a schedule entry runs: the embedding
+    output (the stream as it was before the first entry) and/or one row of a model-wide table."""
+    before: int                    # index into the schedule
+    embedding: bool = False
+    table: str | None = None       # canonical tensor name of a [rows, hidden] table
+    row: int = 0
 
 
 @dataclass(frozen=True)
@@ -126,6 +140,10 @@ class ModelPlan:
     tensor_aliases: Any = None     # callable: checkpoint name -> canonical name (or None)
     unused_tensors: tuple[str, ...] = ()   # canonical names a checkpoint of the architecture may hold that this
                                            # model has no use for (an optional tensor of a part no layer has): skipped
+    stream_adds: tuple[StreamAdd, ...] = ()     # additions to the residual stream between schedule entries
+    stream_tables: dict[str, tuple[int, ...]] = field(default_factory=dict)   # canonical name -> shape of their tables
+    checkpoint_names: Any = None   # callable: canonical name -> name in a checkpoint (the inverse of
+                                   # tensor_aliases; None: "model." in front of everything but the head)
 
     def __post_init__(self):
         n = len(self.layers)
@@ -137,6 +155,12 @@ class ModelPlan:
                 raise ValueError(f"schedule[{i}] names cache entry {c}, outside the schedule")
             if not e.writes_cache and c >= i:
                 raise ValueError(f"schedule[{i}] reads cache entry {c}, which has not run yet")
+        for a in self.stream_adds:
+            if not 0 <= a.before < len(self.schedule):
+                raise ValueError(f"a stream addition names schedule entry {a.before}, outside the schedule")
+            if a.table is not None and (a.table not in self.stream_tables
+                                        or not 0 <= a.row < self.stream_tables[a.table][0]):
+                raise ValueError(f"a stream addition names row {a.row} of '{a.table}', which the plan does not declare")
 
 
 @dataclass
@@ -199,7 +223,7 @@ class Part:
 
 
 class Mixer(Part):
-    def cache_spec(self) -> KVSpec | StateSpec | None:
+    def cache_spec(self) -> KVSpec | StateSpec | tuple | None:
         return None
 
     def forward(self, h, out, accumulate, batch, cache, env) -> None:

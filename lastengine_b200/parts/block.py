@@ -97,3 +97,54 @@ class PreNormResidualBlock:
             self.post_ffn_norm.forward(x, t, add=True)
         env.split_in = env.split_out = None
         return last if last is not None and last.filled else None
+
+
+@BLOCKS.register("gated_pre_norm_residual")
+class GatedPreNormResidualBlock:
+    """x += s1 * Mixer(h1), h1 = norm1(x);  x += s2 * FeedForward(h2), h2 = norm2(x), where each
+    s = gate(h) is computed from the sublayer's own input (parts.gate) and multiplies the sublayer's
+    result element by element; a gate that is absent leaves the plain sum.  A layer may have no
+    feed-forward: it then ends after the first sum.  The residual and both sums are float."""
+
+    def __init__(self, mixer, ffn, mixer_norm, ffn_norm, post_mixer_norm=None, post_ffn_norm=None,
+                 mixer_gate=None, ffn_gate=None):
+        if post_mixer_norm is not None or post_ffn_norm is not None:
+            raise ValueError("the gated arrangement has no norms after its sublayers")
+        if (ffn is None) != (ffn_norm is None):
+            raise ValueError("a feed-forward and its norm come together or not at all")
+        self.mixer, self.ffn = mixer, ffn
+        self.mixer_norm, self.ffn_norm = mixer_norm, ffn_norm
+        self.mixer_gate, self.ffn_gate = mixer_gate, ffn_gate
+
+    def parts(self) -> dict[str, object]:
+        p = {"mixer": self.mixer, "mixer_norm": self.mixer_norm}
+        if self.ffn is not None:
+            p["ffn"], p["ffn_norm"] = self.ffn, self.ffn_norm
+        if self.mixer_gate is not None:
+            p["mixer_gate"] = self.mixer_gate
+        if self.ffn_gate is not None and self.ffn is not None:
+            p["ffn_gate"] = self.ffn_gate
+        return p
+
+    def forward(self, x: torch.Tensor, batch, cache, env, pending=None):
+        M, D = x.shape
+        ws = env.workspace
+        env.split_in = env.split_out = None
+        h = ws.get("block.h", (M, D), env.dtype)
+        self.mixer_norm.forward(h, x)
+        if self.mixer_gate is None:
+            self.mixer.forward(h, x, True, batch, cache, env)
+        else:
+            y = ws.get("block.t", (M, D), torch.float32)
+            self.mixer.forward(h, y, False, batch, cache, env)
+            self.mixer_gate.add_gated(x, y, h, env)
+        if self.ffn is None:
+            return None
+        self.ffn_norm.forward(h, x)
+        if self.ffn_gate is None:
+            self.ffn.forward(h, x, True, batch, env)
+        else:
+            y = ws.get("block.t", (M, D), torch.float32)
+            self.ffn.forward(h, y, False, batch, env)
+            self.ffn_gate.add_gated(x, y, h, env)
+        return None

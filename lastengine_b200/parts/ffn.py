@@ -31,24 +31,37 @@ def fuse_gate_up(w1: torch.Tensor, w3: torch.Tensor, interleave: bool) -> torch.
     return torch.stack([g, u], dim=1).reshape(2 * F_, D).contiguous()
 
 
-@FEED_FORWARDS.register("swiglu")
+_ACTIVATIONS = {"silu": kernels.SILU, "gelu_tanh": kernels.GELU_TANH}
+
+
+@FEED_FORWARDS.register("swiglu", "gated_dense")
 class SwiGLU(FeedForward):
+    """f = W_down (act(W_gate h) * (W_up h)); act is silu (SwiGLU) unless `activation` names another
+    ("gelu_tanh": z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))).  `names`: the three tensors' names
+    under the part's prefix, (gate, up, down)."""
     split_norm = True
 
-    def __init__(self, hidden_size: int, intermediate_size: int):
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu",
+                 names: tuple[str, str, str] = ("w1.weight", "w3.weight", "w2.weight")):
         self.D, self.F = int(hidden_size), int(intermediate_size)
+        if activation not in _ACTIVATIONS:
+            raise ValueError(f"unknown feed-forward activation '{activation}' ({', '.join(sorted(_ACTIVATIONS))})")
+        self.activation = activation
+        self.act = _ACTIVATIONS[activation]
+        self.n_gate, self.n_up, self.n_down = (str(n) for n in names)
         self.w13 = self.w2 = None
         self.fused = False
 
     def tensors(self) -> dict[str, TensorSpec]:
-        return {"w1.weight": TensorSpec((self.F, self.D), MATRIX),
-                "w3.weight": TensorSpec((self.F, self.D), MATRIX),
-                "w2.weight": TensorSpec((self.D, self.F), MATRIX)}
+        return {self.n_gate: TensorSpec((self.F, self.D), MATRIX),
+                self.n_up: TensorSpec((self.F, self.D), MATRIX),
+                self.n_down: TensorSpec((self.D, self.F), MATRIX)}
 
     def load(self, tensors, env: BuildEnv) -> None:
-        self.fused = (not env.is_float32) and self.F % 16 == 0
-        self.w13 = fuse_gate_up(tensors["w1.weight"], tensors["w3.weight"], self.fused)
-        self.w2 = tensors["w2.weight"].contiguous()
+        # the products' fused epilogue is SwiGLU; other activations run as a kernel after the product
+        self.fused = (not env.is_float32) and self.F % 16 == 0 and self.act == kernels.SILU
+        self.w13 = fuse_gate_up(tensors[self.n_gate], tensors[self.n_up], self.fused)
+        self.w2 = tensors[self.n_down].contiguous()
 
     def split_reader_weight(self):
         return self.w13
@@ -63,7 +76,10 @@ class SwiGLU(FeedForward):
         else:
             gu = ws.get("ffn.gu", (M, 2 * self.F), torch.float32)
             kernels.linear(gu, h, self.w13, scale=scale)
-            kernels.swiglu(a, gu)
+            if self.act == kernels.SILU:
+                kernels.swiglu(a, gu)
+            else:
+                kernels.gated_act(a, gu, self.act)
         kernels.linear(out, a, self.w2, kernels.ACCUMULATE if accumulate else kernels.STORE,
                        emit=emit if accumulate else None)
 

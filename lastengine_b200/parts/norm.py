@@ -1,11 +1,15 @@
-"""RMSNorm: y = x / sqrt(mean(x^2) + eps) * w  (src/dense.rs:27-30)."""
+"""RMSNorm: y = x / sqrt(mean(x^2) + eps) * w  (src/dense.rs:27-30).
+
+`offset`: the weight is stored around zero and the factor is offset + w (1 + w in the designs that
+store it so); it is added once, in float, when the weights are loaded.  `tensor`: the weight's name
+under the part's prefix ("" where the prefix itself names it)."""
 from __future__ import annotations
 
 import torch
 
 from ..ops import kernels
 from ..registry import NORMS
-from .base import NORM, BuildEnv, Part, TensorSpec
+from .base import NORM, NORM_AROUND_ZERO, BuildEnv, Part, TensorSpec
 
 
 @NORMS.register("rmsnorm")
@@ -14,16 +18,20 @@ class RMSNorm(Part):
     # before it and r to the product after it (a norm with a mean or a bias could not be split so)
     splittable = True
 
-    def __init__(self, size: int, eps: float):
+    def __init__(self, size: int, eps: float, offset: float = 0.0, tensor: str = "weight"):
         self.size = int(size)
         self.eps = float(eps)
+        self.offset = float(offset)
+        self.tensor = str(tensor)
         self.weight: torch.Tensor | None = None
 
     def tensors(self) -> dict[str, TensorSpec]:
-        return {"weight": TensorSpec((self.size,), NORM)}
+        # a weight stored around zero starts at zero (the factor is then 1), not at one
+        return {self.tensor: TensorSpec((self.size,), NORM if self.offset == 0.0 else NORM_AROUND_ZERO)}
 
     def load(self, tensors: dict[str, torch.Tensor], env: BuildEnv) -> None:
-        self.weight = tensors["weight"].contiguous()
+        w = tensors[self.tensor].to(torch.float32)
+        self.weight = (w + self.offset if self.offset != 0.0 else w).contiguous()
 
     def forward(self, out: torch.Tensor, x: torch.Tensor, rows: torch.Tensor | None = None,
                 add: bool = False) -> None:

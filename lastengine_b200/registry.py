@@ -56,6 +56,7 @@ FEED_FORWARDS = Registry("feed-forward")
 NORMS = Registry("norm")
 POSITION_ENCODINGS = Registry("position encoding")
 BLOCKS = Registry("block arrangement")
+GATES = Registry("sublayer gate")
 EMBEDDINGS = Registry("embedding")
 HEADS = Registry("output head")
 

@@ -15,7 +15,7 @@ import os
 
 import torch
 
-from ..parts.base import BIAS, NORM, ModelPlan, TensorSpec
+from ..parts.base import BIAS, NORM, NORM_AROUND_ZERO, ModelPlan, TensorSpec
 from .safetensors_io import save_file
 
 
@@ -34,6 +34,10 @@ def random_tensor(name: str, spec: TensorSpec, seed: int, std: float, norm_init:
         if norm_init == "ones":
             return torch.ones(spec.shape, dtype=torch.float32, device=dev)
         return 1.0 + 0.1 * torch.randn(spec.shape, generator=g, dtype=torch.float32, device=dev)
+    if spec.role == NORM_AROUND_ZERO:
+        if norm_init == "ones":
+            return torch.zeros(spec.shape, dtype=torch.float32, device=dev)
+        return 0.1 * torch.randn(spec.shape, generator=g, dtype=torch.float32, device=dev)
     s = spec.std if spec.std is not None else std
     if spec.role == BIAS and spec.std is None:
         return torch.zeros(spec.shape, dtype=torch.float32, device=dev)
@@ -54,6 +58,8 @@ def storage_dtype(spec: TensorSpec, dtype: torch.dtype) -> torch.dtype:
 
 def checkpoint_name(plan: ModelPlan, canonical: str) -> str:
     """Name under which a tensor is written: the architecture's checkpoint spelling."""
+    if plan.checkpoint_names is not None:
+        return plan.checkpoint_names(canonical)
     head = plan.names.get("head", "head")
     return canonical if canonical.startswith(head + ".") else "model." + canonical
 
