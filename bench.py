@@ -288,6 +288,130 @@ def _classes(summary: dict, work: dict, unit: str, per: float, peak: float, wher
     return rows
 
 
+# ---- the Zekivik design beside the LFM3 hybrid at equal layer sizes (--compare zekivik) -------------------
+def zekivik_config(width: int, ff: int, heads: int, kv_heads: int, dim: int, vdim: int, ret_heads: int,
+                   ret_dim: int, ret_vdim: int, layers: int, vocab: int) -> dict:
+    """Layers alternate retention and attention, every layer with a feed-forward; the first two run twice."""
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": 4, "scale": dim ** -0.5,
+           "rot": {"dims": dim, "base": 1000000.0}}
+    ret = {"heads": ret_heads, "dim": ret_dim, "vdim": ret_vdim,
+           "decay": [1.0 - 2.0 ** (-5 - (i % 8)) for i in range(ret_heads)], "rot": {"dims": ret_dim, "base": 10000.0}}
+    ls = [{"type": "retention" if i % 2 == 0 else "attention", "mixer": ret if i % 2 == 0 else att,
+           "mlp": {"kind": "dense", "ff": ff}} for i in range(layers)]
+    return {"architecture": "Zekivik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "layers": ls,
+            "loop": {"start": 0, "stop": 2, "times": 2}}
+
+
+def lfm3_like(width: int, ff: int, heads: int, kv_heads: int, dim: int, runs: int, vocab: int) -> dict:
+    """The closest existing design at the same sizes: as many layer runs, short convolution where the
+    other has retention, the same attention and feed-forward widths."""
+    return {"architectures": ["Lfm3ForCausalLM"], "model_type": "lfm3", "vocab_size": vocab, "hidden_size": width,
+            "num_hidden_layers": runs, "layer_types": ["conv" if i % 2 == 0 else "attention" for i in range(runs)],
+            "num_attention_heads": heads, "num_key_value_heads": kv_heads, "head_dim": dim, "intermediate_size": ff,
+            "block_auto_adjust_ff_dim": False, "rope_theta": 1000000.0, "conv_L_cache": 4, "norm_eps": 1e-5,
+            "tie_embedding": False, "max_position_embeddings": 128000}
+
+
+COMPARE_SIZES = {   # width, ff, heads, kv heads, head size, value head size, retention heads / key size / value size, layers
+    "w2048": dict(width=2048, ff=5632, heads=32, kv_heads=8, dim=64, vdim=64, ret_heads=16, ret_dim=128, ret_vdim=128, layers=6),
+    "w1024": dict(width=1024, ff=4096, heads=16, kv_heads=4, dim=64, vdim=64, ret_heads=8, ret_dim=64, ret_vdim=128, layers=6),
+    "w2048-v32": dict(width=2048, ff=5632, heads=32, kv_heads=8, dim=64, vdim=32, ret_heads=32, ret_dim=32, ret_vdim=64, layers=6),
+}
+
+# what a launch of the new design's own kernels has to move, per row of the step (bytes) -- for the roofline of
+# the memory-bound ones; the products and the attention kernels are the ones the other design runs too
+def _new_kernel_bytes(cfg: dict, rows: int, batch: int) -> dict:
+    W = cfg["width"]
+    out = {"leb_gated_residual": 0, "leb_gated_act": 0, "leb_stream_add": 0, "leb_causal_conv": 0, "leb_retention": 0}
+    runs = []
+    lp = cfg["loop"]
+    for i, l in enumerate(cfg["layers"]):
+        runs += [l] * (lp["times"] if lp["start"] <= i < lp["stop"] else 1)
+    for l in runs:
+        m = l["mixer"]
+        n_sub = 2 if l["mlp"] else 1
+        out["leb_gated_residual"] += n_sub * rows * W * 16                     # x read and written, y and z read (float)
+        if l["mlp"]:
+            out["leb_gated_act"] += rows * l["mlp"]["ff"] * (8 + 2)            # gate and up (float) in, bfloat16 out
+        if l["type"] == "attention":
+            C = (m["heads"] + m["kv_heads"]) * m["dim"] + m["kv_heads"] * m["vdim"]
+            out["leb_causal_conv"] += rows * C * 4 + batch * C * (m["conv"] - 1) * 8
+        else:
+            H, d, e = m["heads"], m["dim"], m["vdim"]
+            out["leb_retention"] += rows * H * (2 * d + 3 * e) * 2 + batch * H * d * e * 8
+    out["leb_stream_add"] = lp["times"] * rows * W * 12
+    return out
+
+
+def compare_designs(which: str, steps: int, warmup: int) -> int:
+    import numpy as np
+    import torch
+    from lastengine_b200 import Engine
+    from lastengine_b200.ops import kernels
+    pk, pk_src = peaks()
+    rng = np.random.default_rng(0)
+    results = {}
+    for size_name, sz in COMPARE_SIZES.items():
+        zc = zekivik_config(vocab=32768, **sz)
+        runs = sz["layers"] + 2
+        lc = lfm3_like(sz["width"], sz["ff"], sz["heads"], sz["kv_heads"], sz["dim"], runs, 32768)
+        row = {}
+        for label, cfg in (("zekivik", zc), ("lfm3", lc)):
+            eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=8 * 2304 + 4096, max_seqs=16)
+            nums = model_numbers(eng)
+            r = {"weights_gb": round(nums["weight_bytes"] / 1e9, 3)}
+            pre_ms = time_prefill(eng, PREFILL_TOKENS, 3, 5, rng)
+            flops = (PREFILL_TOKENS * nums["linear_flops_per_token"] + nums["head_flops_per_row"]
+                     + nums["attn_flops_per_qk"] * PREFILL_TOKENS * (PREFILL_TOKENS + 1) // 2)
+            r["prefill_2048_ms"] = pre_ms
+            r["prefill_tok_s"] = PREFILL_TOKENS / (pre_ms / 1e3)
+            r["prefill_frac_of_bf16_peak"] = flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12)
+            for b in (1, 8):
+                d = time_decode(eng, b, 2048, steps, warmup, rng)
+                r[f"decode_b{b}_ms"] = d["ms_per_step"]
+                r[f"decode_b{b}_tok_s"] = d["tok_s"]
+                r[f"decode_b{b}_launches"] = d["launches_per_step"]
+                r[f"decode_b{b}_frac_of_hbm"] = decode_step_bytes(eng, nums, b, d["avg_context"]) / (d["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"]
+            # every entry point of a prompt and of a decode step, one after the other under the event timer
+            toks = rng.integers(0, eng.vocab_size, size=PREFILL_TOKENS).tolist()
+            s = eng.new_sequence()
+            eng.step([s], [toks], "last")
+            eng.release(s)
+            s = eng.new_sequence()
+            torch.cuda.synchronize()
+            with kernels.KernelTimer(head_start_ms=5.0) as t:
+                eng.step([s], [toks], "last")
+            eng.release(s)
+            pre_k = t.summary()
+            seqs = fill_context(eng, 8, 2046, rng)
+            eng.step(seqs, [[1]] * 8, "last")
+            torch.cuda.synchronize()
+            with kernels.KernelTimer(head_start_ms=5.0) as t:
+                eng.step(seqs, [[2]] * 8, "last")
+            eng.release(seqs)
+            dec_k = t.summary()
+            by = {"prefill": _new_kernel_bytes(zc, PREFILL_TOKENS, 1), "decode_b8": _new_kernel_bytes(zc, 8, 8)} if label == "zekivik" else {}
+            for where, summ in (("prefill", pre_k), ("decode_b8", dec_k)):
+                ks = {}
+                for name, (calls, ms) in summ.items():
+                    e = {"launches": calls, "ms": round(ms, 4)}
+                    nb = by.get(where, {}).get(name)
+                    if nb and ms > 0:
+                        e["gb_s"] = round(nb / (ms / 1e3) / 1e9, 1)
+                        e["frac_of_hbm"] = round(nb / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 3)
+                    ks[name] = e
+                r[f"kernels_{where}"] = ks
+            row[label] = r
+            del eng
+            torch.cuda.empty_cache()
+        results[size_name] = {"sizes": sz, **row}
+    print(json.dumps({"compare": which, "against": "lfm3 hybrid at equal layer sizes", "dtype": "bf16",
+                      "data": "synthetic (random weights, uniform random token ids)", "peaks": pk_src,
+                      "prefill_tokens": PREFILL_TOKENS, "decode_context": 2048, "steps": steps, "warmup": warmup,
+                      "sizes": results}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -306,8 +430,13 @@ def main() -> int:
     ap.add_argument("--unequal", type=int, default=0, metavar="N",
                     help="instead of the contract's run: N requests with prompts of U[64, 2048] tokens generate "
                          "--steps tokens each in one batch through the Python entry point (prints its own JSON line)")
+    ap.add_argument("--compare", default="", choices=["", "zekivik"],
+                    help="instead of the contract's run: prefill and decode of that design at a few layer sizes beside "
+                         "the LFM3 hybrid at equal sizes, with every kernel's time (prints its own JSON line)")
     args = ap.parse_args()
 
+    if args.compare:
+        return compare_designs(args.compare, min(args.steps, 128), max(args.warmup, 3))
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "the reference is a Rust crate (cargo, NVRTC); no Rust toolchain here, pip cannot install it "

@@ -140,3 +140,358 @@ LEB_API int leb_retention(void* out, const void* q, const void* k, const void* v
 #undef LEB_RET_T
 #undef LEB_RET
 }
+
+// ---------------------------------------------------------------------------------------------
+// The chunked form, for steps with many rows per sequence.  A sequence's rows are cut into chunks
+// of RC rows.  With g = decay, L the rows of chunk c and S_c the state before its first row:
+//   U_c = sum_j g^(L-1-j) k_j v_j^T                                   (kernel 1, every chunk at once)
+//   S_{c+1} = g^L S_c + U_c, S_0 = the sequence's state               (kernel 2, a thread per state element)
+//   o_i = sum_{j<=i} g^(i-j) (q_i . k_j) v_j + g^(i+1) S_c^T q_i      (kernel 3, every chunk at once)
+// followed by the per-head norm and the gate as in the recurrent form.  All of it is float on the
+// CUDA cores: scores, decay powers (by repeated multiplication, as the recurrence forms them),
+// state and sums; only the order of the sums differs from the recurrent form.
+constexpr int RC = 64;            // rows of a chunk
+constexpr int RCT = 256;          // threads of a chunk's block
+
+// (sequence, chunk within it, first row, rows) of chunk number `gidx` of the step, or false past the last
+__device__ __forceinline__ bool find_chunk(int gidx, const int* seq_qlen, int B, int& b, int& c, int& nrows, int& base) {
+  int acc = 0;
+  for (int s = 0; s < B; s++) {
+    const int n = seq_qlen[s];
+    const int nc = (n + RC - 1) / RC;
+    if (gidx < acc + nc) {
+      b = s;
+      c = gidx - acc;
+      nrows = min(RC, n - c * RC);
+      base = acc;
+      return true;
+    }
+    acc += nc;
+  }
+  return false;
+}
+
+// Rotated q and k (k scaled, and weighted by wk[j] if given) and v of a chunk into shared memory,
+// rows past the chunk's end as zeros.  ldq/ldv: padded row lengths in shared memory.
+template <typename T>
+__device__ __forceinline__ void stage_chunk(float* qs, float* ks, float* vs, int ldq, int ldv, const T* q, const T* k,
+                                            const T* v, int ld, size_t row0, int nrows, int pos0, int h, int d, int e,
+                                            const float* inv_freq, int rot, float k_scale, const float* wk) {
+  const int half = rot / 2;
+  const int npair = half + (d - rot);       // rotated pairs, then the dimensions that pass unchanged
+  for (int idx = threadIdx.x; idx < RC * npair; idx += blockDim.x) {
+    const int i = idx / npair, p = idx - i * npair;
+    const bool in = i < nrows;
+    const T* qr = q + (row0 + i) * ld + (size_t)h * d;
+    const T* kr = k + (row0 + i) * ld + (size_t)h * d;
+    const float w = k_scale * (wk ? wk[i] : 1.f);
+    if (p < half) {
+      float qa = 0.f, qb = 0.f, ka = 0.f, kb = 0.f;
+      if (in) {
+        float sn, cs;
+        sincosf((float)(pos0 + i) * inv_freq[p], &sn, &cs);
+        const float a = to_f32(qr[p]), bb = to_f32(qr[p + half]), a2 = to_f32(kr[p]), b2 = to_f32(kr[p + half]);
+        qa = a * cs - bb * sn;
+        qb = bb * cs + a * sn;
+        ka = (a2 * cs - b2 * sn) * w;
+        kb = (b2 * cs + a2 * sn) * w;
+      }
+      if (qs) { qs[i * ldq + p] = qa; qs[i * ldq + p + half] = qb; }
+      ks[i * ldq + p] = ka;
+      ks[i * ldq + p + half] = kb;
+    } else {
+      const int j = rot + (p - half);
+      if (qs) qs[i * ldq + j] = in ? to_f32(qr[j]) : 0.f;
+      ks[i * ldq + j] = in ? to_f32(kr[j]) * w : 0.f;
+    }
+  }
+  for (int idx = threadIdx.x; idx < RC * e; idx += blockDim.x) {
+    const int i = idx / e, j = idx - i * e;
+    vs[i * ldv + j] = i < nrows ? to_f32(v[(row0 + i) * ld + (size_t)h * e + j]) : 0.f;
+  }
+}
+
+// Kernel 1: U_c [d][e] of every chunk.  scratch [chunk][H][d][e].
+template <typename T>
+__global__ void __launch_bounds__(RCT) retention_chunk_state_kernel(
+    float* __restrict__ scratch, const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int ld,
+    const float* __restrict__ decay, const float* __restrict__ inv_freq, int rot, float k_scale,
+    const int* __restrict__ seq_pos0, const int* __restrict__ seq_qstart, const int* __restrict__ seq_qlen,
+    int B, int H, int d, int e) {
+  extern __shared__ float sm[];
+  pdl_trigger();
+  pdl_wait();
+  int b, c, nrows, base;
+  if (!find_chunk(blockIdx.x, seq_qlen, B, b, c, nrows, base)) return;
+  const int h = blockIdx.y;
+  const int d8 = (d + 7) & ~7, e8 = (e + 7) & ~7;
+  float* ks = sm;                    // [RC][d8]
+  float* vs = ks + RC * d8;          // [RC][e8]
+  float* wk = vs + RC * e8;          // [RC]  g^(L-1-j)
+  const float g = decay[h];
+  if (threadIdx.x == 0) {
+    float p = 1.f;
+    for (int j = nrows - 1; j >= 0; j--) { wk[j] = p; p *= g; }
+    for (int j = nrows; j < RC; j++) wk[j] = 0.f;
+  }
+  for (int idx = threadIdx.x; idx < RC * (d8 - d); idx += blockDim.x) ks[(idx / (d8 - d)) * d8 + d + idx % (d8 - d)] = 0.f;
+  for (int idx = threadIdx.x; idx < RC * (e8 - e); idx += blockDim.x) vs[(idx / (e8 - e)) * e8 + e + idx % (e8 - e)] = 0.f;
+  __syncthreads();
+  stage_chunk<T>(nullptr, ks, vs, d8, e8, q, k, v, ld, (size_t)seq_qstart[b] + (size_t)c * RC, nrows,
+                 seq_pos0[b] + c * RC, h, d, e, inv_freq, rot, k_scale, wk);
+  __syncthreads();
+  float* out = scratch + ((size_t)(base + c) * H + h) * d * e;
+  const int te = e8 / 8, tiles = (d8 / 8) * te;
+  for (int t = threadIdx.x; t < tiles; t += blockDim.x) {
+    const int r0 = (t / te) * 8, c0 = (t % te) * 8;
+    float acc[8][8];
+#pragma unroll
+    for (int a = 0; a < 8; a++)
+#pragma unroll
+      for (int bb = 0; bb < 8; bb++) acc[a][bb] = 0.f;
+    for (int j = 0; j < nrows; j++) {
+      const float4 k0 = *reinterpret_cast<const float4*>(ks + j * d8 + r0), k1 = *reinterpret_cast<const float4*>(ks + j * d8 + r0 + 4);
+      const float4 v0 = *reinterpret_cast<const float4*>(vs + j * e8 + c0), v1 = *reinterpret_cast<const float4*>(vs + j * e8 + c0 + 4);
+      const float kk[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
+      const float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+      for (int a = 0; a < 8; a++)
+#pragma unroll
+        for (int bb = 0; bb < 8; bb++) acc[a][bb] += kk[a] * vv[bb];
+    }
+#pragma unroll
+    for (int a = 0; a < 8; a++)
+#pragma unroll
+      for (int bb = 0; bb < 8; bb++)
+        if (r0 + a < d && c0 + bb < e) out[(size_t)(r0 + a) * e + c0 + bb] = acc[a][bb];
+  }
+}
+
+// Kernel 2: the states before every chunk, in place of the U_c, and the sequence's state after the step.
+__global__ void __launch_bounds__(256) retention_chunk_scan_kernel(
+    float* __restrict__ scratch, float* __restrict__ state, const float* __restrict__ decay,
+    const int* __restrict__ seq_slot, const int* __restrict__ seq_qlen, int B, int H, int de) {
+  pdl_trigger();
+  pdl_wait();
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int x = blockIdx.x * blockDim.x + threadIdx.x;
+  if (x >= de) return;
+  int base = 0;
+  for (int s = 0; s < b; s++) base += (seq_qlen[s] + RC - 1) / RC;
+  const int n = seq_qlen[b], nc = (n + RC - 1) / RC;
+  const int slot = seq_slot[b];
+  const float g = decay[h];
+  float gl = 1.f;                                  // g^RC, by repeated multiplication
+  for (int j = 0; j < RC; j++) gl *= g;
+  float* sp = slot >= 0 ? state + ((size_t)slot * H + h) * de + x : nullptr;
+  float S = sp ? *sp : 0.f;
+  for (int c = 0; c < nc; c++) {
+    float* u = scratch + ((size_t)(base + c) * H + h) * de + x;
+    const float U = *u;
+    *u = S;
+    float gp = gl;
+    if (c == nc - 1 && n - c * RC < RC) {
+      gp = 1.f;
+      for (int j = 0; j < n - c * RC; j++) gp *= g;
+    }
+    S = gp * S + U;
+  }
+  if (sp) *sp = S;
+}
+
+// Kernel 3: the chunk's outputs.
+template <typename T>
+__global__ void __launch_bounds__(RCT) retention_chunk_out_kernel(
+    T* __restrict__ out, const float* __restrict__ scratch, const T* __restrict__ q, const T* __restrict__ k,
+    const T* __restrict__ v, const T* __restrict__ gt, int ld, const float* __restrict__ decay,
+    const float* __restrict__ inv_freq, int rot, float k_scale, float eps, const int* __restrict__ seq_pos0,
+    const int* __restrict__ seq_qstart, const int* __restrict__ seq_qlen, int B, int H, int d, int e) {
+  extern __shared__ float sm[];
+  pdl_trigger();
+  pdl_wait();
+  int b, c, nrows, base;
+  if (!find_chunk(blockIdx.x, seq_qlen, B, b, c, nrows, base)) return;
+  const int h = blockIdx.y;
+  const int d8 = (d + 7) & ~7, e8 = (e + 7) & ~7;
+  float* qs = sm;                    // [RC][d8]
+  float* ks = qs + RC * d8;          // [RC][d8], later slabs of the state [rows][e8]
+  float* vs = ks + RC * d8;          // [RC][e8]
+  float* as = vs + RC * e8;          // [RC][RC + 1] decayed scores
+  float* pw = as + RC * (RC + 1);    // [RC + 1] powers of the decay
+  const float g = decay[h];
+  if (threadIdx.x == 0) {
+    float p = 1.f;
+    for (int j = 0; j <= RC; j++) { pw[j] = p; p *= g; }
+  }
+  for (int idx = threadIdx.x; idx < RC * (d8 - d); idx += blockDim.x) {
+    const int o = (idx / (d8 - d)) * d8 + d + idx % (d8 - d);
+    qs[o] = 0.f;
+    ks[o] = 0.f;
+  }
+  for (int idx = threadIdx.x; idx < RC * (e8 - e); idx += blockDim.x) vs[(idx / (e8 - e)) * e8 + e + idx % (e8 - e)] = 0.f;
+  const size_t row0 = (size_t)seq_qstart[b] + (size_t)c * RC;
+  stage_chunk<T>(qs, ks, vs, d8, e8, q, k, v, ld, row0, nrows, seq_pos0[b] + c * RC, h, d, e, inv_freq, rot, k_scale,
+                 nullptr);
+  __syncthreads();
+  // decayed scores A[i][j] = (q_i . k_j) g^(i-j), j <= i: a thread takes 4 x 4 of them
+  {
+    const int i0 = (threadIdx.x / 16) * 4, j0 = (threadIdx.x % 16) * 4;
+    float acc[4][4] = {};
+    if (j0 <= i0 + 3) {
+      for (int r = 0; r < d8; r += 4) {
+        float4 qa[4], kb[4];
+#pragma unroll
+        for (int a = 0; a < 4; a++) {
+          qa[a] = *reinterpret_cast<const float4*>(qs + (i0 + a) * d8 + r);
+          kb[a] = *reinterpret_cast<const float4*>(ks + (j0 + a) * d8 + r);
+        }
+#pragma unroll
+        for (int a = 0; a < 4; a++)
+#pragma unroll
+          for (int bb = 0; bb < 4; bb++)
+            acc[a][bb] += qa[a].x * kb[bb].x + qa[a].y * kb[bb].y + qa[a].z * kb[bb].z + qa[a].w * kb[bb].w;
+      }
+    }
+#pragma unroll
+    for (int a = 0; a < 4; a++)
+#pragma unroll
+      for (int bb = 0; bb < 4; bb++) {
+        const int i = i0 + a, j = j0 + bb;
+        as[i * (RC + 1) + j] = j <= i ? acc[a][bb] * pw[i - j] : 0.f;
+      }
+  }
+  __syncthreads();       // the scores are written, and nobody reads ks any more: it takes the state's slabs
+  // o[i][c] for a thread's 4 rows x 8 columns per tile: the chunk's own keys, then the state before the chunk
+  const int te = e8 / 8, tiles = (RC / 4) * te;
+  const float* Sg = scratch + ((size_t)(base + c) * H + h) * d * e;
+  const int slab = max(1, min(d, (RC * d8) / e8));          // rows of the state that fit where ks was
+  float acc[2][4][8];                                        // up to two tiles per thread (e <= 256: tiles <= 512)
+#pragma unroll
+  for (int u = 0; u < 2; u++)
+#pragma unroll
+    for (int a = 0; a < 4; a++)
+#pragma unroll
+      for (int bb = 0; bb < 8; bb++) acc[u][a][bb] = 0.f;
+#pragma unroll
+  for (int u = 0; u < 2; u++) {
+    const int t = threadIdx.x + u * RCT;
+    if (t >= tiles) break;
+    const int i0 = (t / te) * 4, c0 = (t % te) * 8;
+    for (int j = 0; j < min(nrows, i0 + 4); j++) {
+      const float4 v0 = *reinterpret_cast<const float4*>(vs + j * e8 + c0), v1 = *reinterpret_cast<const float4*>(vs + j * e8 + c0 + 4);
+      const float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+      for (int a = 0; a < 4; a++) {
+        const float s = as[(i0 + a) * (RC + 1) + j];
+#pragma unroll
+        for (int bb = 0; bb < 8; bb++) acc[u][a][bb] += s * vv[bb];
+      }
+    }
+  }
+  // the rows of q times their power of the decay, once, so that the state's part is a plain product
+  for (int idx = threadIdx.x; idx < RC * d8; idx += blockDim.x) qs[idx] *= pw[idx / d8 + 1];
+  for (int r0 = 0; r0 < d; r0 += slab) {
+    const int nr = min(slab, d - r0);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nr * e8; idx += blockDim.x) {
+      const int r = idx / e8, cc = idx - r * e8;
+      ks[idx] = cc < e ? Sg[(size_t)(r0 + r) * e + cc] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int u = 0; u < 2; u++) {
+      const int t = threadIdx.x + u * RCT;
+      if (t >= tiles) break;
+      const int i0 = (t / te) * 4, c0 = (t % te) * 8;
+      for (int r = 0; r < nr; r++) {
+        const float4 s0 = *reinterpret_cast<const float4*>(ks + r * e8 + c0), s1 = *reinterpret_cast<const float4*>(ks + r * e8 + c0 + 4);
+        const float ss[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+        for (int a = 0; a < 4; a++) {
+          const float qv = qs[(i0 + a) * d8 + r0 + r];
+#pragma unroll
+          for (int bb = 0; bb < 8; bb++) acc[u][a][bb] += qv * ss[bb];
+        }
+      }
+    }
+  }
+  __syncthreads();       // everyone is done with vs: the outputs go there, [RC][e8]
+#pragma unroll
+  for (int u = 0; u < 2; u++) {
+    const int t = threadIdx.x + u * RCT;
+    if (t >= tiles) break;
+    const int i0 = (t / te) * 4, c0 = (t % te) * 8;
+#pragma unroll
+    for (int a = 0; a < 4; a++)
+#pragma unroll
+      for (int bb = 0; bb < 8; bb++) vs[(i0 + a) * e8 + c0 + bb] = acc[u][a][bb];
+  }
+  __syncthreads();
+  // per row: the head's root mean square, the gate, the store
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = warp; i < nrows; i += RCT / 32) {
+    float ssq = 0.f;
+    for (int j = lane; j < e; j += 32) ssq += vs[i * e8 + j] * vs[i * e8 + j];
+    ssq = warp_sum(ssq);
+    const float r = 1.0f / sqrtf(ssq / (float)e + eps);
+    const size_t m = row0 + i;
+    for (int j = lane; j < e; j += 32) {
+      const float gz = to_f32(gt[m * ld + (size_t)h * e + j]);
+      out[m * (size_t)(H * e) + (size_t)h * e + j] = from_f32<T>(vs[i * e8 + j] * r * (gz / (1.0f + expf(-gz))));
+    }
+  }
+}
+
+// Floats of scratch the chunked form needs for a step of M rows in B sequences.
+LEB_API long long leb_retention_chunked_scratch(int M, int B, int H, int d, int e) {
+  return ((long long)M / RC + B) * H * d * e;
+}
+LEB_API int leb_retention_chunked_supported(int d, int e) { return d >= 1 && e >= 1 && d <= 256 && e <= 256; }
+
+LEB_API int leb_retention_chunked(void* out, const void* q, const void* k, const void* v, const void* g, int ld, int dtype,
+                                  float* state, float* scratch, const float* decay, const float* inv_freq, int rot,
+                                  float k_scale, float eps, const int* seq_slot, const int* seq_pos0,
+                                  const int* seq_qstart, const int* seq_qlen, int M, int B, int H, int d, int e,
+                                  cudaStream_t st) {
+  if (M <= 0 || B <= 0) return 0;
+  LEB_REQUIRE(dtype == LEB_F32 || dtype == LEB_BF16, "leb_retention_chunked: unknown dtype %d", dtype);
+  LEB_REQUIRE(leb_retention_chunked_supported(d, e), "leb_retention_chunked: head sizes %d x %d outside 1..256", d, e);
+  LEB_REQUIRE(rot >= 0 && rot <= d && rot % 2 == 0, "leb_retention_chunked: %d rotated dimensions do not fit %d", rot, d);
+  LEB_REQUIRE(seq_qlen && scratch, "leb_retention_chunked: needs the sequences' row counts and scratch");
+  LEB_REQUIRE(B <= 65535 && H <= 65535, "leb_retention_chunked: %d sequences, %d heads", B, H);
+  const int d8 = (d + 7) & ~7, e8 = (e + 7) & ~7;
+  const int chunks = M / RC + B;       // at least as many as the step has
+  const size_t smem1 = (size_t)(RC * d8 + RC * e8 + RC) * sizeof(float);
+  const size_t smem3 = (size_t)(2 * RC * d8 + RC * e8 + RC * (RC + 1) + RC + 1) * sizeof(float);
+#define LEB_RC_ATTR(kern, bytes)                                                                              \
+  if ((bytes) > 48 * 1024) {                                                                                  \
+    cudaError_t er = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(bytes));   \
+    if (er != cudaSuccess) return leb_fail("leb_retention_chunked: shared memory %zu: %s", (size_t)(bytes), cudaGetErrorString(er)); \
+  }
+  if (dtype == LEB_F32) {
+    LEB_RC_ATTR(retention_chunk_state_kernel<float>, smem1);
+    LEB_RC_ATTR(retention_chunk_out_kernel<float>, smem3);
+    leb_launch(retention_chunk_state_kernel<float>, dim3(chunks, H), dim3(RCT), smem1, st, scratch, (const float*)q,
+               (const float*)k, (const float*)v, ld, decay, inv_freq, rot, k_scale, seq_pos0, seq_qstart, seq_qlen, B, H, d, e);
+  } else {
+    LEB_RC_ATTR(retention_chunk_state_kernel<bf16>, smem1);
+    LEB_RC_ATTR(retention_chunk_out_kernel<bf16>, smem3);
+    leb_launch(retention_chunk_state_kernel<bf16>, dim3(chunks, H), dim3(RCT), smem1, st, scratch, (const bf16*)q,
+               (const bf16*)k, (const bf16*)v, ld, decay, inv_freq, rot, k_scale, seq_pos0, seq_qstart, seq_qlen, B, H, d, e);
+  }
+  LEB_CHECK_LAUNCH("leb_retention_chunked states");
+  leb_launch(retention_chunk_scan_kernel, dim3(ceil_div(d * e, 256), H, B), dim3(256), 0, st, scratch, state, decay,
+             seq_slot, seq_qlen, B, H, d * e);
+  LEB_CHECK_LAUNCH("leb_retention_chunked scan");
+  if (dtype == LEB_F32)
+    leb_launch(retention_chunk_out_kernel<float>, dim3(chunks, H), dim3(RCT), smem3, st, (float*)out, (const float*)scratch,
+               (const float*)q, (const float*)k, (const float*)v, (const float*)g, ld, decay, inv_freq, rot, k_scale, eps,
+               seq_pos0, seq_qstart, seq_qlen, B, H, d, e);
+  else
+    leb_launch(retention_chunk_out_kernel<bf16>, dim3(chunks, H), dim3(RCT), smem3, st, (bf16*)out, (const float*)scratch,
+               (const bf16*)q, (const bf16*)k, (const bf16*)v, (const bf16*)g, ld, decay, inv_freq, rot, k_scale, eps,
+               seq_pos0, seq_qstart, seq_qlen, B, H, d, e);
+  LEB_CHECK_LAUNCH("leb_retention_chunked outputs");
+#undef LEB_RC_ATTR
+  return 0;
+}

@@ -105,6 +105,8 @@ def _declare(L) -> None:
         "leb_stream_add": [P, P, P, I, I, P],
         "leb_causal_conv": [P, I, P, I, I, P, P, P, P, P, P, I, I, I, I, I, P],
         "leb_retention": [P, P, P, P, P, I, I, P, P, P, I, F, F, P, P, P, P, I, I, I, I, I, P],
+        "leb_retention_chunked": [P, P, P, P, P, I, I, P, P, P, P, I, F, F, P, P, P, P, I, I, I, I, I, P],
+        "leb_retention_chunked_supported": [I, I],
         "leb_gemm_f32": [P, P, P, I, I, I, I, I, I, P, I, S, P],
         "leb_gemm_bf16_small": [P, I, P, P, I, I, I, I, I, I, P, I, S, I, P],
         "leb_gemm_bf16_stream": [P, I, P, P, I, I, I, I, I, I, P, I, I, F, P, P, P, P],
@@ -149,6 +151,8 @@ def _declare(L) -> None:
     L.leb_launch_count.argtypes = []
     L.leb_sm_count.restype = c_int
     L.leb_sm_count.argtypes = []
+    L.leb_retention_chunked_scratch.restype = ctypes.c_longlong
+    L.leb_retention_chunked_scratch.argtypes = [I, I, I, I, I]
     for name, args in _OPTIONAL.items():
         fn = getattr(L, name, None)
         if fn is not None:
@@ -298,6 +302,18 @@ def causal_conv(y: torch.Tensor, u: torch.Tensor, w: torch.Tensor, state: torch.
                                  M, batch.n_seqs, C, taps, 1 if single else 0, _stream()))
 
 
+RETENTION_CHUNKED_MIN_ROWS = 16     # longest row count of a sequence from which a step runs the chunked form
+_retention_ws: dict[int, list[torch.Tensor]] = {}
+
+
+def _retention_workspace(device: torch.device, n_floats: int) -> torch.Tensor:
+    """Float scratch for the chunk states; grows by adding buffers and never frees one (captured graphs)."""
+    bufs = _retention_ws.setdefault(_device_index(device), [])
+    if not bufs or bufs[-1].numel() < n_floats:
+        bufs.append(torch.empty(max(n_floats, 1 << 20), dtype=torch.float32, device=device))
+    return bufs[-1]
+
+
 def retention(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
               state: torch.Tensor, decay: torch.Tensor, inv_freq: torch.Tensor | None, rot: int, k_scale: float,
               eps: float, batch, H: int, d: int, e: int) -> None:
@@ -319,7 +335,16 @@ def retention(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tens
         _cuda(inv_freq, "retention.inv_freq", torch.float32)
         assert inv_freq.numel() == rot // 2
     single = batch.max_qlen == 1 and M == batch.n_seqs
-    _check(lib().leb_retention(_ptr(out), _ptr(q), _ptr(k), _ptr(v), _ptr(g), ld, _dt(out, "retention"), _ptr(state),
+    L = lib()
+    if batch.max_qlen >= RETENTION_CHUNKED_MIN_ROWS and L.leb_retention_chunked_supported(d, e):
+        # many rows per sequence: chunks of the sequences side by side, the states between them by a scan
+        scratch = _retention_workspace(out.device, int(L.leb_retention_chunked_scratch(M, batch.n_seqs, H, d, e)))
+        _check(L.leb_retention_chunked(_ptr(out), _ptr(q), _ptr(k), _ptr(v), _ptr(g), ld, _dt(out, "retention"),
+                                       _ptr(state), _ptr(scratch), _ptr(decay), _ptr(inv_freq), int(rot), float(k_scale),
+                                       float(eps), _ptr(batch.seq_slot), _ptr(batch.seq_pos0), _ptr(batch.seq_qstart),
+                                       _ptr(batch.seq_qlen), M, batch.n_seqs, H, d, e, _stream()))
+        return
+    _check(L.leb_retention(_ptr(out), _ptr(q), _ptr(k), _ptr(v), _ptr(g), ld, _dt(out, "retention"), _ptr(state),
                                _ptr(decay), _ptr(inv_freq), int(rot), float(k_scale), float(eps), _ptr(batch.seq_slot),
                                _ptr(batch.seq_pos0), _ptr(batch.seq_qstart), None if single else _ptr(batch.seq_qlen),
                                M, batch.n_seqs, H, d, e, _stream()))
