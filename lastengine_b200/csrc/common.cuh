@@ -55,6 +55,22 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
   if (sizeof(T) == 2) return __fdividef(g, 1.0f + __expf(-g)) * u;
   return g / (1.0f + expf(-g)) * u;
 }
+// A gated epilogue (code 2: act(gate) * up over interleaved weight rows) names its activation in the
+// upper bits of the epilogue code the kernels get: 0 silu, 1 the tanh form of gelu.  The entry
+// points take the same combined code, check it, and hand it on through LEB_EPI_ARG at the launch.
+extern thread_local int g_leb_gate_act;
+#define LEB_EPI_ARG(e) ((e) | (g_leb_gate_act << 8))
+template <typename T>
+__device__ __forceinline__ float gate_mul(float g, float u, int act) {
+  if (act == 1) {
+    const float z = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    float t;
+    if (sizeof(T) == 2) asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(z));   // as silu_mul: far below bfloat16 rounding
+    else t = tanhf(z);
+    return 0.5f * g * (1.0f + t) * u;
+  }
+  return silu_mul<T>(g, u);
+}
 // Device side.  pdl_trigger(): the next kernel on the stream may be scheduled (once every block
 // of this one has said so); it then runs its own start-up and waits in its pdl_wait() until this
 // kernel has completed.  Said first thing, even before this kernel's own wait: a product two

@@ -18,6 +18,7 @@ LEB_API const char* leb_last_error() { return g_err; }
 
 long long g_leb_launches = 0;
 int g_leb_pdl = 1;
+thread_local int g_leb_gate_act = 0;
 LEB_API void leb_set_pdl(int on) { g_leb_pdl = on ? 1 : 0; }
 LEB_API long long leb_launch_count() { return g_leb_launches; }
 
@@ -264,30 +265,47 @@ LEB_API int leb_gated_act(void* a, int out_dtype, const void* gu, int in_dtype, 
 
 // ---------------------------------------------------------------------------------------------
 // The gated residual: x[m, i] += y[m, i] * sigmoid(z[m, i] + b[i]); x, y and b are float, the gate's
-// pre-activation z comes from a matrix product in float or bfloat16.  Sum and sigmoid are float.
-template <typename TZ>
-__global__ void gated_residual_kernel(float* __restrict__ x, const float* __restrict__ y,
-                                      const TZ* __restrict__ z, const float* __restrict__ b, int D, size_t total) {
+// pre-activation z comes from a matrix product in float or bfloat16 (row stride ldz: it may be a
+// column range of a wider result).  Sum and sigmoid are float.  With `h` the same launch also
+// leaves the RMS norm of the new row, h = x / sqrt(mean(x^2) + eps) * w, for the sublayer that reads
+// the stream next (a block per row; the row is read back from cache for the second pass).
+template <typename TZ, typename TH>
+__global__ void __launch_bounds__(256) gated_residual_kernel(
+    float* __restrict__ x, const float* __restrict__ y, const TZ* __restrict__ z, int ldz,
+    const float* __restrict__ b, TH* __restrict__ h, const float* __restrict__ w, float eps, int D) {
+  __shared__ float red[33];
   pdl_trigger();
   pdl_wait();
-  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= total) return;
-  int c = (int)(i % D);
-  float zz = to_f32(z[i]) + (b ? b[c] : 0.f);
-  x[i] += y[i] * (1.0f / (1.0f + expf(-zz)));
+  const size_t m = blockIdx.x;
+  float* xr = x + m * D;
+  const float* yr = y + m * D;
+  const TZ* zr = z + m * ldz;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    const float zz = to_f32(zr[i]) + (b ? b[i] : 0.f);
+    const float v = xr[i] + yr[i] * (1.0f / (1.0f + expf(-zz)));
+    xr[i] = v;
+    ss += v * v;
+  }
+  if (!h) return;
+  ss = block_sum(ss, red);
+  const float r = 1.0f / sqrtf(ss / (float)D + eps);
+  TH* hr = h + m * D;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) hr[i] = from_f32<TH>(xr[i] * r * w[i]);   // a thread re-reads what it wrote
 }
 
-LEB_API int leb_gated_residual(float* x, const float* y, const void* z, int z_dtype, const float* b, int M, int D,
-                               cudaStream_t st) {
-  size_t total = (size_t)M * D;
-  if (total == 0) return 0;
-  dim3 grid((unsigned)((total + 255) / 256)), block(256);
-  if (z_dtype == LEB_F32)
-    leb_launch(gated_residual_kernel<float>, grid, block, 0, st, x, y, (const float*)z, b, D, total);
-  else if (z_dtype == LEB_BF16)
-    leb_launch(gated_residual_kernel<bf16>, grid, block, 0, st, x, y, (const bf16*)z, b, D, total);
-  else
-    return leb_fail("leb_gated_residual: unknown dtype %d", z_dtype);
+LEB_API int leb_gated_residual(float* x, const float* y, const void* z, int ldz, int z_dtype, const float* b, void* h,
+                               int h_dtype, const float* w, float eps, int M, int D, cudaStream_t st) {
+  if (M <= 0 || D <= 0) return 0;
+  LEB_REQUIRE(!h || w, "leb_gated_residual: a norm needs its weight");
+  const dim3 grid(M), block(D >= 1024 ? 256 : 128);
+#define LEB_GR(TZ, TH) leb_launch(gated_residual_kernel<TZ, TH>, grid, block, 0, st, x, y, (const TZ*)z, ldz, b, (TH*)h, w, eps, D)
+  if (z_dtype == LEB_F32 && (!h || h_dtype == LEB_F32)) LEB_GR(float, float);
+  else if (z_dtype == LEB_F32 && h_dtype == LEB_BF16) LEB_GR(float, bf16);
+  else if (z_dtype == LEB_BF16 && (!h || h_dtype == LEB_BF16)) LEB_GR(bf16, bf16);
+  else if (z_dtype == LEB_BF16 && h_dtype == LEB_F32) LEB_GR(bf16, float);
+  else return leb_fail("leb_gated_residual: unknown dtypes z=%d h=%d", z_dtype, h_dtype);
+#undef LEB_GR
   LEB_CHECK_LAUNCH("leb_gated_residual");
   return 0;
 }

@@ -37,6 +37,8 @@ __global__ void __launch_bounds__(32 * SM_WARPS)
 gemm_bf16_small_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf16* __restrict__ W,
                        int M, int N, int K, int lda, int ldc, int epilogue,
                        const int* __restrict__ group_offsets, size_t w_group_stride) {
+  const int act = epilogue >> 8;   // the gated epilogue's activation rides in the upper bits
+  epilogue &= 255;
   __shared__ float red[SM_WARPS][NSUB][SM_ROWS][8 * MT + 1];
   int row_begin = 0, row_end = M;
   const int n0 = blockIdx.x * (SM_ROWS * NSUB);
@@ -142,7 +144,7 @@ gemm_bf16_small_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf1
         g += red[w][0][i][col];
         u += red[w][NSUB - 1][i][col];
       }
-      C[(size_t)m * ldc + jbase + i] = from_f32<TC>(silu_mul<TC>(g, u));
+      C[(size_t)m * ldc + jbase + i] = from_f32<TC>(gate_mul<TC>(g, u, act));
     }
     return;
   }
@@ -171,7 +173,7 @@ static int launch_small(void* C, const bf16* A, const bf16* W, int M, int N, int
   dim3 block(32 * SM_WARPS);
 #define LEB_SM(MT_, U_)                                                                          \
   leb_launch(gemm_bf16_small_kernel<TC, MT_, NSUB, U_>, grid, block, 0, st, (TC*)C, A, W, M, N, K, lda, \
-             ldc, epilogue, group_offsets, w_group_stride)
+             ldc, LEB_EPI_ARG(epilogue), group_offsets, w_group_stride)
   switch (mt) {
     case 1: {
       // blocks resident per SM for each depth (asked once), and the SM count
@@ -206,6 +208,10 @@ LEB_API int leb_gemm_bf16_small(void* C, int c_dtype, const void* A, const void*
                                 int K, int lda, int ldc, int epilogue, const int* group_offsets,
                                 int n_groups, size_t w_group_stride, int rows_hint,
                                 cudaStream_t st) {
+  const int act_ = epilogue >> 8;
+  epilogue &= 255;
+  LEB_REQUIRE(act_ == 0 || (act_ == 1 && epilogue == 2), "leb_gemm_bf16_small: activation %d goes with the gated epilogue only", act_);
+  g_leb_gate_act = act_;
   if (M <= 0 || N <= 0) return 0;
   LEB_REQUIRE(K > 0 && K % 8 == 0, "leb_gemm_bf16_small: K (%d) must be a multiple of 8", K);
   LEB_REQUIRE(lda % 8 == 0, "leb_gemm_bf16_small: row stride of A (%d) must be a multiple of 8", lda);

@@ -33,6 +33,8 @@ template <typename TC, int MT, int NSUB, int S, int ST_WARPS>
 __global__ void __launch_bounds__(32 * ST_WARPS)
 gemm_bf16_stream_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf16* __restrict__ W,
                         int M, int N, int K, int lda, int ldc, int epilogue, int n_tiles, StreamConv cv, StreamNorm nm) {
+  const int act = epilogue >> 8;   // the gated epilogue's activation rides in the upper bits
+  epilogue &= 255;
   constexpr int ROWS = ST_ROWS * NSUB, XOFF = ROWS * 128, STAGE = (ROWS + 8 * MT) * 128;
   constexpr bool CONV = NSUB == 3;   // the only user of three sub-tiles
   const int D3 = N / 3;
@@ -256,7 +258,7 @@ gemm_bf16_stream_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf
         }
         gt *= row_scale[col];
         up *= row_scale[col];
-        C[(size_t)col * ldc + jbase + i] = from_f32<TC>(silu_mul<TC>(gt, up));
+        C[(size_t)col * ldc + jbase + i] = from_f32<TC>(gate_mul<TC>(gt, up, act));
       }
     } else {
       const int n0 = tile * ROWS;
@@ -304,6 +306,8 @@ __global__ void __launch_bounds__(32 * ST_WARPS, 2)
 gemm_bf16_stream_grouped_kernel(TC* __restrict__ C, const bf16* __restrict__ A, const bf16* __restrict__ W, int N,
                                 int K, int lda, int ldc, int epilogue, const int* __restrict__ group_offsets,
                                 int n_groups, size_t w_group_stride) {
+  const int act = epilogue >> 8;   // the gated epilogue's activation rides in the upper bits
+  epilogue &= 255;
   constexpr int ROWS = ST_ROWS * NSUB, XOFF = ROWS * 128, STAGE = (ROWS + 8 * MT) * 128;
   extern __shared__ __align__(128) unsigned char st_smem[];
   __shared__ int cum[ST_MAX_GROUPS + 1], offs[ST_MAX_GROUPS + 1];
@@ -434,7 +438,7 @@ gemm_bf16_stream_grouped_kernel(TC* __restrict__ C, const bf16* __restrict__ A, 
           gt += red[w][0][i][col];
           up += red[w][NSUB - 1][i][col];
         }
-        C[(size_t)(ct.row0 + col) * ldc + jbase + i] = from_f32<TC>(silu_mul<TC>(gt, up));
+        C[(size_t)(ct.row0 + col) * ldc + jbase + i] = from_f32<TC>(gate_mul<TC>(gt, up, act));
       }
     } else {
       for (int idx = threadIdx.x; idx < ROWS * 8 * MT; idx += blockDim.x) {
@@ -474,7 +478,7 @@ static int launch_stream_grouped(void* C, const bf16* A, const bf16* W, int P, i
   const long most = ((long)ceil_div(P, 8 * MT) + n_groups) * ceil_div(N, ROWS);
   const int grid = (int)(most < slots ? most : slots);
   leb_launch(gemm_bf16_stream_grouped_kernel<TC, MT, NSUB, S, ST_WARPS>, dim3(grid), dim3(32 * ST_WARPS), smem, st,
-             (TC*)C, A, W, N, K, lda, ldc, epilogue, group_offsets, n_groups, w_group_stride);
+             (TC*)C, A, W, N, K, lda, ldc, LEB_EPI_ARG(epilogue), group_offsets, n_groups, w_group_stride);
   LEB_CHECK_LAUNCH("leb_gemm_bf16_stream_grouped");
   return 0;
 }
@@ -499,7 +503,7 @@ static int launch_stream(void* C, const bf16* A, const bf16* W, int M, int N, in
   const int per_block = ceil_div(n_tiles, slots);
   const int grid = ceil_div(n_tiles, per_block);
   leb_launch(gemm_bf16_stream_kernel<TC, MT, NSUB, S, ST_WARPS>, dim3(grid), dim3(32 * ST_WARPS), smem, st, (TC*)C, A, W, M, N,
-             K, lda, ldc, epilogue, n_tiles, cv, nm);
+             K, lda, ldc, LEB_EPI_ARG(epilogue), n_tiles, cv, nm);
   LEB_CHECK_LAUNCH("leb_gemm_bf16_stream");
   return 0;
 }
@@ -523,6 +527,10 @@ static int stream_dispatch(void* C, const bf16* a, const bf16* w, int M, int N, 
 LEB_API int leb_gemm_bf16_stream(void* C, int c_dtype, const void* A, const void* W, int M, int N, int K, int lda,
                                  int ldc, int epilogue, const float* ssq_in, int parts_in, int d_in, float eps,
                                  void* emit_vals, const float* emit_g, float* emit_ssq, cudaStream_t st) {
+  const int act_ = epilogue >> 8;
+  epilogue &= 255;
+  LEB_REQUIRE(act_ == 0 || (act_ == 1 && epilogue == 2), "leb_gemm_bf16_stream: activation %d goes with the gated epilogue only", act_);
+  g_leb_gate_act = act_;
   if (M <= 0 || N <= 0) return 0;
   LEB_REQUIRE(M <= 16, "leb_gemm_bf16_stream: %d rows; this kernel takes at most 16", M);
   LEB_REQUIRE(K > 0 && K % 8 == 0, "leb_gemm_bf16_stream: K (%d) must be a multiple of 8", K);
@@ -546,6 +554,7 @@ LEB_API int leb_gemm_bf16_stream_conv(void* y, const void* A, const void* W, int
                                       const float* conv_w, const float* bias, float* state, const int* row_seq,
                                       const int* seq_slot, int Lc, const float* ssq_in, int parts_in, int d_in,
                                       float eps, cudaStream_t st) {
+  g_leb_gate_act = 0;   // no gated epilogue here
   if (M <= 0 || D <= 0) return 0;
   LEB_REQUIRE(M <= 16, "leb_gemm_bf16_stream_conv: %d rows; this kernel takes at most 16", M);
   LEB_REQUIRE(K > 0 && K % 8 == 0 && lda % 8 == 0, "leb_gemm_bf16_stream_conv: K (%d) and the row stride of A (%d) must be multiples of 8", K, lda);
@@ -576,6 +585,10 @@ static int stream_grouped_dispatch(void* C, const bf16* a, const bf16* w, int P,
 LEB_API int leb_gemm_bf16_stream_grouped(void* C, int c_dtype, const void* A, const void* W, int P, int N, int K,
                                          int lda, int ldc, int epilogue, const int* group_offsets, int n_groups,
                                          size_t w_group_stride, cudaStream_t st) {
+  const int act_ = epilogue >> 8;
+  epilogue &= 255;
+  LEB_REQUIRE(act_ == 0 || (act_ == 1 && epilogue == 2), "leb_gemm_bf16_stream_grouped: activation %d goes with the gated epilogue only", act_);
+  g_leb_gate_act = act_;
   if (P <= 0 || N <= 0 || n_groups <= 0) return 0;
   LEB_REQUIRE(n_groups <= ST_MAX_GROUPS, "leb_gemm_bf16_stream_grouped: %d groups; at most %d", n_groups, ST_MAX_GROUPS);
   LEB_REQUIRE(K > 0 && K % 8 == 0 && lda % 8 == 0, "leb_gemm_bf16_stream_grouped: K (%d) and the row stride of A (%d) must be multiples of 8", K, lda);

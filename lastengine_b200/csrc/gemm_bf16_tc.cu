@@ -39,6 +39,8 @@ __global__ void __launch_bounds__(TC_THREADS)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     TC* __restrict__ C_all, int M, int N, int K, int ldc, int epilogue, int* __restrict__ status,
                     const int* __restrict__ group_offsets, int n_groups) {
+  const int act = epilogue >> 8;   // the gated epilogue's activation rides in the upper bits
+  epilogue &= 255;
   __shared__ int g_cum[GROUPED ? TC_MAX_GROUPS + 1 : 1], g_off[GROUPED ? TC_MAX_GROUPS + 1 : 1];
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment for the swizzled tiles
@@ -232,7 +234,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
             for (int e = 0; e < 4; e++) {
               const float g = __uint_as_float(v[i + e]), u = __uint_as_float(v[16 + i + e]);
-              fp[e] = silu_mul<TC>(g, u);
+              fp[e] = gate_mul<TC>(g, u, act);
             }
             *reinterpret_cast<float4*>(mine + i) = f;
           }
@@ -328,7 +330,7 @@ static int launch_tc(void* C, const CUtensorMap& ma, const CUtensorMap& mw, int 
   // grouped: the most tiles the offsets can give (every expert may end with a partly filled tile)
   const long tiles = (long)ceil_div(N, BN) * (ceil_div(M, TC_BM) + (GROUPED ? n_groups : 0)) * (!GROUPED && n_groups > 1 ? n_groups : 1);
   dim3 grid((unsigned)(tiles < n_sm ? tiles : n_sm));
-  leb_launch(kern, grid, dim3(TC_THREADS), smem, st, ma, mw, (TC*)C, M, N, K, ldc, epilogue, status, group_offsets,
+  leb_launch(kern, grid, dim3(TC_THREADS), smem, st, ma, mw, (TC*)C, M, N, K, ldc, LEB_EPI_ARG(epilogue), status, group_offsets,
              n_groups);
   LEB_CHECK_LAUNCH("leb_gemm_bf16_tc");
   return 0;
@@ -343,6 +345,10 @@ LEB_API int leb_gemm_bf16_tc_supported(const void* A, const void* W, int K, int 
 // status: device int, set non-zero by a block whose bounded wait gave up.
 LEB_API int leb_gemm_bf16_tc(void* C, int c_dtype, const void* A, const void* W, int M, int N, int K, int lda,
                              int ldc, int epilogue, int* status, cudaStream_t st) {
+  const int act_ = epilogue >> 8;
+  epilogue &= 255;
+  LEB_REQUIRE(act_ == 0 || (act_ == 1 && epilogue == 2), "leb_gemm_bf16_tc: activation %d goes with the gated epilogue only", act_);
+  g_leb_gate_act = act_;
   if (M <= 0 || N <= 0) return 0;
   LEB_REQUIRE(leb_gemm_bf16_tc_supported(A, W, K, lda), "leb_gemm_bf16_tc: operands not aligned for TMA (K %d, lda %d)", K, lda);
   LEB_REQUIRE(epilogue >= 0 && epilogue <= 2, "leb_gemm_bf16_tc: unknown epilogue %d", epilogue);
@@ -397,6 +403,10 @@ LEB_API int leb_gemm_bf16_tc_slices(int M, int N, int K) {
 // slice order and applies the epilogue.
 LEB_API int leb_gemm_bf16_tc_sliced(void* C, int c_dtype, const void* A, const void* W, int M, int N, int K, int lda,
                                     int ldc, int epilogue, float* part, int n_slices, int* status, cudaStream_t st) {
+  const int act_ = epilogue >> 8;
+  epilogue &= 255;
+  LEB_REQUIRE(act_ == 0 || (act_ == 1 && epilogue == 2), "leb_gemm_bf16_tc_sliced: activation %d goes with the gated epilogue only", act_);
+  g_leb_gate_act = act_;
   if (M <= 0 || N <= 0) return 0;
   LEB_REQUIRE(leb_gemm_bf16_tc_supported(A, W, K, lda), "leb_gemm_bf16_tc_sliced: operands not aligned for TMA (K %d, lda %d)", K, lda);
   LEB_REQUIRE(epilogue >= 0 && epilogue <= 2, "leb_gemm_bf16_tc_sliced: unknown epilogue %d", epilogue);
@@ -420,6 +430,10 @@ LEB_API int leb_gemm_bf16_tc_sliced(void* C, int c_dtype, const void* A, const v
 LEB_API int leb_gemm_bf16_tc_grouped(void* C, int c_dtype, const void* A, const void* W, int P, int N, int K, int lda,
                                      int ldc, int epilogue, const int* group_offsets, int n_groups, int* status,
                                      cudaStream_t st) {
+  const int act_ = epilogue >> 8;
+  epilogue &= 255;
+  LEB_REQUIRE(act_ == 0 || (act_ == 1 && epilogue == 2), "leb_gemm_bf16_tc_grouped: activation %d goes with the gated epilogue only", act_);
+  g_leb_gate_act = act_;
   if (P <= 0 || N <= 0 || n_groups <= 0) return 0;
   LEB_REQUIRE(n_groups <= TC_MAX_GROUPS, "leb_gemm_bf16_tc_grouped: %d groups; at most %d", n_groups, TC_MAX_GROUPS);
   LEB_REQUIRE(leb_gemm_bf16_tc_supported(A, W, K, lda), "leb_gemm_bf16_tc_grouped: operands not aligned for TMA (K %d, lda %d)", K, lda);

@@ -68,6 +68,8 @@ template <typename TC>
 __global__ void __launch_bounds__(T2_THREADS)
 gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                      TC* __restrict__ C, int M, int N, int K, int ldc, int epilogue, int* __restrict__ status) {
+  const int act = epilogue >> 8;   // the gated epilogue's activation rides in the upper bits
+  epilogue &= 255;
   constexpr int BN = T2_BN, STAGES = T2_STAGES;
   constexpr int A_BYTES = 128 * TC_BK * 2, B_BYTES = 128 * TC_BK * 2;   // this block's halves
   extern __shared__ uint8_t smem_raw[];
@@ -204,7 +206,7 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 #pragma unroll
               for (int e = 0; e < 4; e++) {
                 const float g = __uint_as_float(v[i + e]), u = __uint_as_float(v[16 + i + e]);
-                fp[e] = silu_mul<TC>(g, u);
+                fp[e] = gate_mul<TC>(g, u, act);
               }
               *reinterpret_cast<float4*>(mine + i) = f;
             }
@@ -311,7 +313,7 @@ static int launch_tc2(void* C, const CUtensorMap& ma, const CUtensorMap& mw, int
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = g_leb_pdl ? 2 : 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ma, mw, (TC*)C, M, N, K, ldc, epilogue, status);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ma, mw, (TC*)C, M, N, K, ldc, LEB_EPI_ARG(epilogue), status);
   if (e != cudaSuccess) return leb_fail("leb_gemm_bf16_tc2: %s", cudaGetErrorString(e));
   LEB_CHECK_LAUNCH("leb_gemm_bf16_tc2");
   return 0;
@@ -321,6 +323,10 @@ static int launch_tc2(void* C, const CUtensorMap& ma, const CUtensorMap& mw, int
 // and status word as leb_gemm_bf16_tc.
 LEB_API int leb_gemm_bf16_tc2(void* C, int c_dtype, const void* A, const void* W, int M, int N, int K, int lda,
                               int ldc, int epilogue, int* status, cudaStream_t st) {
+  const int act_ = epilogue >> 8;
+  epilogue &= 255;
+  LEB_REQUIRE(act_ == 0 || (act_ == 1 && epilogue == 2), "leb_gemm_bf16_tc2: activation %d goes with the gated epilogue only", act_);
+  g_leb_gate_act = act_;
   if (M <= 0 || N <= 0) return 0;
   LEB_REQUIRE(K > 0 && K % 8 == 0 && lda % 8 == 0 && ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0,
               "leb_gemm_bf16_tc2: operands not aligned for TMA (K %d, lda %d)", K, lda);

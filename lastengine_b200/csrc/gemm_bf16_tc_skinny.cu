@@ -37,6 +37,8 @@ __global__ void __launch_bounds__(SK_THREADS, SK_STAGES <= 4 ? 2 : 1)
 gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                       float* __restrict__ part, void* __restrict__ C, int c_dtype, int M, int N, int K, int ldc,
                       int epilogue, int n_slices, int* __restrict__ status, FinishNorm nm) {
+  const int act = epilogue >> 8;   // the gated epilogue's activation rides in the upper bits
+  epilogue &= 255;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   __shared__ float row_scale[MP];
@@ -174,7 +176,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             const float gt = __uint_as_float(v[i]) * rs;
             const float up = __shfl_down_sync(0xffffffffu, gt, 16);
             if (lane < 16 && c0 + i < M && 2 * j < N) {
-              const float a = c_dtype == LEB_F32 ? silu_mul<float>(gt, up) : silu_mul<bf16>(gt, up);
+              const float a = c_dtype == LEB_F32 ? gate_mul<float>(gt, up, act) : gate_mul<bf16>(gt, up, act);
               if (c_dtype == LEB_F32) ((float*)C)[(size_t)(c0 + i) * ldc + j] = a;
               else ((bf16*)C)[(size_t)(c0 + i) * ldc + j] = __float2bfloat16_rn(a);
             }
@@ -248,6 +250,8 @@ template <typename TC>
 __global__ void __launch_bounds__(256)
 skinny_finish_kernel(TC* __restrict__ C, const float* __restrict__ part, int M, int N, int ldc, int epilogue,
                      int n_slices, FinishNorm nm, FinishConv cv) {
+  const int act = epilogue >> 8;   // the gated epilogue's activation rides in the upper bits
+  epilogue &= 255;
   pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
   const int m = blockIdx.y;
@@ -304,7 +308,7 @@ skinny_finish_kernel(TC* __restrict__ C, const float* __restrict__ part, int M, 
     const int n = 32 * (j >> 4) + (j & 15);
     const float g = sum_slices(part + (size_t)m * N + n, slab, n_slices) * r;
     const float u = sum_slices(part + (size_t)m * N + n + 16, slab, n_slices) * r;
-    C[(size_t)m * ldc + j] = from_f32<TC>(silu_mul<TC>(g, u));
+    C[(size_t)m * ldc + j] = from_f32<TC>(gate_mul<TC>(g, u, act));
     return;
   }
   const bool in = j < N;
@@ -331,9 +335,9 @@ int leb_slices_finish(void* C, int c_dtype, const float* part, int M, int N, int
   const int cols = epilogue == 2 ? N / 2 : N;
   dim3 grid(ceil_div(cols, 256), M);
   if (c_dtype == LEB_F32)
-    leb_launch(skinny_finish_kernel<float>, grid, dim3(256), 0, st, (float*)C, part, M, N, ldc, epilogue, n_slices, FinishNorm{}, FinishConv{});
+    leb_launch(skinny_finish_kernel<float>, grid, dim3(256), 0, st, (float*)C, part, M, N, ldc, LEB_EPI_ARG(epilogue), n_slices, FinishNorm{}, FinishConv{});
   else if (c_dtype == LEB_BF16)
-    leb_launch(skinny_finish_kernel<bf16>, grid, dim3(256), 0, st, (bf16*)C, part, M, N, ldc, epilogue, n_slices, FinishNorm{}, FinishConv{});
+    leb_launch(skinny_finish_kernel<bf16>, grid, dim3(256), 0, st, (bf16*)C, part, M, N, ldc, LEB_EPI_ARG(epilogue), n_slices, FinishNorm{}, FinishConv{});
   else
     return leb_fail("leb_slices_finish: unknown C dtype %d", c_dtype);
   LEB_CHECK_LAUNCH("leb_slices_finish");
@@ -353,7 +357,7 @@ static int launch_skinny(const CUtensorMap& mw, const CUtensorMap& mx, float* pa
     set = true;
   }
   dim3 grid(ceil_div(N, 128), n_slices);
-  cudaError_t e = leb_launch(kern, grid, dim3(SK_THREADS), smem, st, mw, mx, part, C, c_dtype, M, N, K, ldc, epilogue,
+  cudaError_t e = leb_launch(kern, grid, dim3(SK_THREADS), smem, st, mw, mx, part, C, c_dtype, M, N, K, ldc, LEB_EPI_ARG(epilogue),
                              n_slices, status, nm);
   if (e != cudaSuccess) return leb_fail("leb_gemm_bf16_skinny: %s", cudaGetErrorString(e));
   LEB_CHECK_LAUNCH("leb_gemm_bf16_skinny");
@@ -409,9 +413,9 @@ static int skinny_product(void* C, int c_dtype, const void* A, const void* W, in
   const int cols = epilogue == 2 ? N / 2 : (epilogue == 3 ? N / 3 : N);
   dim3 grid(ceil_div(cols, 256), M);
   if (c_dtype == LEB_F32)
-    leb_launch(skinny_finish_kernel<float>, grid, dim3(256), 0, st, (float*)C, (const float*)part, M, N, ldc, epilogue, n_slices, nm, cv);
+    leb_launch(skinny_finish_kernel<float>, grid, dim3(256), 0, st, (float*)C, (const float*)part, M, N, ldc, LEB_EPI_ARG(epilogue), n_slices, nm, cv);
   else if (c_dtype == LEB_BF16)
-    leb_launch(skinny_finish_kernel<bf16>, grid, dim3(256), 0, st, (bf16*)C, (const float*)part, M, N, ldc, epilogue, n_slices, nm, cv);
+    leb_launch(skinny_finish_kernel<bf16>, grid, dim3(256), 0, st, (bf16*)C, (const float*)part, M, N, ldc, LEB_EPI_ARG(epilogue), n_slices, nm, cv);
   else
     return leb_fail("leb_gemm_bf16_skinny: unknown C dtype %d", c_dtype);
   LEB_CHECK_LAUNCH("leb_gemm_bf16_skinny finish");
@@ -422,6 +426,10 @@ LEB_API int leb_gemm_bf16_skinny(void* C, int c_dtype, const void* A, const void
                                  int ldc, int epilogue, float* part, int n_slices, const float* ssq_in, int parts_in,
                                  int d_in, float eps, void* emit_vals, const float* emit_g, float* emit_ssq, int* status,
                                  cudaStream_t st) {
+  const int act_ = epilogue >> 8;
+  epilogue &= 255;
+  LEB_REQUIRE(act_ == 0 || (act_ == 1 && epilogue == 2), "leb_gemm_bf16_skinny: activation %d goes with the gated epilogue only", act_);
+  g_leb_gate_act = act_;
   if (M <= 0 || N <= 0) return 0;
   LEB_REQUIRE(leb_gemm_bf16_skinny_supported(A, W, M, K, lda), "leb_gemm_bf16_skinny: takes 1..128 rows and TMA-aligned operands (M %d, K %d, lda %d)", M, K, lda);
   LEB_REQUIRE(epilogue >= 0 && epilogue <= 2, "leb_gemm_bf16_skinny: unknown epilogue %d", epilogue);
@@ -442,6 +450,7 @@ LEB_API int leb_gemm_bf16_skinny_conv(void* y, const void* A, const void* W, int
                                       const float* conv_w, const float* bias, float* state, const int* row_seq,
                                       const int* seq_slot, int Lc, float* part, int n_slices, const float* ssq_in,
                                       int parts_in, int d_in, float eps, int* status, cudaStream_t st) {
+  g_leb_gate_act = 0;   // no gated epilogue here
   if (M <= 0 || D <= 0) return 0;
   LEB_REQUIRE(leb_gemm_bf16_skinny_supported(A, W, M, K, lda), "leb_gemm_bf16_skinny_conv: takes 1..128 rows and TMA-aligned operands (M %d, K %d, lda %d)", M, K, lda);
   LEB_REQUIRE(Lc >= 2 && Lc <= SK_CONV_MAX_LC, "leb_gemm_bf16_skinny_conv: conv length %d outside 2..%d", Lc, SK_CONV_MAX_LC);

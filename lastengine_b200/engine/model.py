@@ -112,7 +112,9 @@ class Model:
                 pending = None      # a norm half left for this block was taken from the stream as it was before
             after = self.blocks[sched[i + 1].layer] if i + 1 < len(sched) else None
             # (norm, part that reads it) of the block that runs next, for blocks that can split a norm
-            env.next_block_norm = after.first_reader() if hasattr(after, "first_reader") else None
+            # (nothing is offered across an addition to the stream: the norm would be of the stream before it)
+            env.next_block_norm = after.first_reader() if hasattr(after, "first_reader") and (i + 1) not in self.stream_adds \
+                else None
             if pending is not None:
                 pending = block.forward(x, batch, view, env, pending=pending)
             else:

@@ -101,7 +101,7 @@ def _declare(L) -> None:
         "leb_qk_rope_store": [P, P, I, P, P, I, P, P, I, P, I, P, P, P, P, P, F, P, I, I, I, I, I, I, I, I, I, P],
         "leb_attention": [P, P, P, P, P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, I, P],
         "leb_gated_act": [P, I, P, I, I, I, I, P],
-        "leb_gated_residual": [P, P, P, I, P, I, I, P],
+        "leb_gated_residual": [P, P, P, I, I, P, P, I, P, F, I, I, P],
         "leb_stream_add": [P, P, P, I, I, P],
         "leb_causal_conv": [P, I, P, I, I, P, P, P, P, P, P, I, I, I, I, I, P],
         "leb_retention": [P, P, P, P, P, I, I, P, P, P, I, F, F, P, P, P, P, I, I, I, I, I, P],
@@ -255,17 +255,26 @@ def gated_act(out: torch.Tensor, gu: torch.Tensor, act: int) -> None:
                                int(act), _stream()))
 
 
-def gated_residual(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor, bias: torch.Tensor | None) -> None:
-    """x += y * sigmoid(z + bias): x and y float [M, D], z the gate's pre-activation [M, D], bias float [D]."""
+def gated_residual(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor, bias: torch.Tensor | None,
+                   h: torch.Tensor | None = None, norm_w: torch.Tensor | None = None, eps: float = 0.0) -> None:
+    """x += y * sigmoid(z + bias): x and y float [M, D], z the gate's pre-activation [M, D] (a column
+    slice is fine), bias float [D].  With `h` [M, D] the launch also leaves there the RMS norm of the
+    new rows with the weight `norm_w` (the input of whatever reads the stream next)."""
     _cuda(x, "gated_residual.x", torch.float32)
     _cuda(y, "gated_residual.y", torch.float32)
-    _cuda(z, "gated_residual.z")
+    _cuda(z, "gated_residual.z", contiguous=False)
     M, D = x.shape
-    assert y.shape == (M, D) and z.shape == (M, D)
+    assert y.shape == (M, D) and z.shape == (M, D) and z.stride(1) == 1
     if bias is not None:
         _cuda(bias, "gated_residual.bias", torch.float32)
         assert bias.numel() == D
-    _check(lib().leb_gated_residual(_ptr(x), _ptr(y), _ptr(z), _dt(z, "gated_residual.z"), _ptr(bias), M, D, _stream()))
+    if h is not None:
+        _cuda(h, "gated_residual.h")
+        _cuda(norm_w, "gated_residual.norm_w", torch.float32)
+        assert h.shape == (M, D) and norm_w.numel() == D
+    _check(lib().leb_gated_residual(_ptr(x), _ptr(y), _ptr(z), z.stride(0), _dt(z, "gated_residual.z"), _ptr(bias),
+                                    _ptr(h), _dt(h, "gated_residual.h") if h is not None else F32, _ptr(norm_w),
+                                    float(eps), M, D, _stream()))
 
 
 def stream_add(x: torch.Tensor, x0: torch.Tensor | None, vec: torch.Tensor | None) -> None:
@@ -674,6 +683,7 @@ def _attention_decode_raw(out, raw: RawQKV, k_pool, v_pool, block_table, batch, 
 
 # ----------------------------------------------------------------------------------------------
 STORE, ACCUMULATE, SWIGLU = 0, 1, 2
+GEGLU = SWIGLU | (GELU_TANH << 8)     # the gated epilogue with the tanh form of gelu: the activation rides in the upper bits
 SMALL_M = 16  # rows up to which the weight-streaming kernel is used; above, tcgen05 tiles
 
 
@@ -754,14 +764,15 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int = 
         N, Kw = w.shape
         E, stride = 1, 0
     assert Kw == K, f"linear: x has {K} columns, w has {Kw}"
-    n_out = N // 2 if epilogue == SWIGLU else N
+    gated = (epilogue & 255) == SWIGLU
+    n_out = N // 2 if gated else N
     assert out.shape == (M, n_out), f"linear: out is {tuple(out.shape)}, expected {(M, n_out)}"
     if M == 0:
         return
     L = lib()
     if x.dtype == torch.float32:
-        if epilogue == SWIGLU:
-            raise KernelError("linear: the float path keeps SwiGLU as its own kernel")
+        if gated:
+            raise KernelError("linear: the float path keeps the gated activation as its own kernel")
         if out.dtype != torch.float32:
             raise KernelError("linear: float operands need a float result")
         _check(L.leb_gemm_f32(_ptr(out), _ptr(x), _ptr(w), M, N, K, lda, ldc, epilogue, _ptr(group_offsets),

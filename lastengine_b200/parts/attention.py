@@ -64,6 +64,7 @@ class AttentionMixer(Mixer):
         pos = position or PartSpec("none")
         self.position = POSITION_ENCODINGS.get(pos.kind)(**pos.params)
         self.w_in = self.w_out = self.q_norm_w = self.k_norm_w = None
+        self.n_extra, self.extra_out = 0, None
 
     def tensors(self) -> dict[str, TensorSpec]:
         D, nh, nkv, hd, vd, n = self.D, self.nh, self.nkv, self.hd, self.vd, self.n
@@ -116,6 +117,15 @@ class AttentionMixer(Mixer):
     def split_reader_weight(self):
         return self.w_in
 
+    def absorb_input_rows(self, w: torch.Tensor) -> bool:
+        """Takes the rows of another product over the same input (a gate on this mixer's result) into
+        the fused projection; every forward then leaves their result in `extra_out` [rows, len(w)]."""
+        if not self.own_kv or w.dtype != self.w_in.dtype or w.shape[1] != self.D or self.n_extra:
+            return False
+        self.w_in = torch.cat([self.w_in, w], dim=0).contiguous()
+        self.n_extra = int(w.shape[0])
+        return True
+
     def flops_per_query_key(self) -> int:
         return 2 * self.nh * (self.hd + self.vd)    # a score and a weighted value, a multiply-add each, per head and dimension
 
@@ -127,7 +137,7 @@ class AttentionMixer(Mixer):
         scale, emit = env.take_split_in(), env.take_split_out()
         writes = self.own_kv and cache.writable
         if self.own_kv and not cache.writable:
-            w_in = self.w_in[: nh * hd] if not self.output_gate else None
+            w_in = self.w_in[: nh * hd] if not (self.output_gate or self.n_extra) else None
         else:
             w_in = self.w_in
         if w_in is None:  # q and gate rows are not adjacent once k, v are skipped: two products
@@ -143,6 +153,8 @@ class AttentionMixer(Mixer):
             col += nkv * (hd + vd)
         if self.output_gate:
             gate = proj[:, col: col + nh]
+        if self.n_extra:
+            self.extra_out = proj[:, proj.shape[1] - self.n_extra:]
         if self.taps:
             # q, k and v (not the gate) through the short convolution; the state moves on by the step's rows
             if not writes:

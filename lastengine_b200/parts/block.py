@@ -99,12 +99,27 @@ class PreNormResidualBlock:
         return last if last is not None and last.filled else None
 
 
+class NormedRows:
+    """The norm of the residual stream as a block left it for the block after it."""
+
+    filled = False      # not the half of a split norm: a block that splits norms passes it by
+
+    def __init__(self, values: torch.Tensor, norm):
+        self.values, self.norm = values, norm
+
+
 @BLOCKS.register("gated_pre_norm_residual")
 class GatedPreNormResidualBlock:
     """x += s1 * Mixer(h1), h1 = norm1(x);  x += s2 * FeedForward(h2), h2 = norm2(x), where each
     s = gate(h) is computed from the sublayer's own input (parts.gate) and multiplies the sublayer's
     result element by element; a gate that is absent leaves the plain sum.  A layer may have no
-    feed-forward: it then ends after the first sum.  The residual and both sums are float."""
+    feed-forward: it then ends after the first sum.  The residual and both sums are float.
+
+    Fused steps: the kernel that adds a gated result into x also leaves the norm of the new x for the
+    sublayer that follows (in this block, or the first of the next block when that is of this
+    arrangement too and nothing is added to the stream in between), so a layer runs one norm kernel
+    at most; and a mixer that can (`absorb_input_rows`) forms the gate's product R h in its own
+    first product."""
 
     def __init__(self, mixer, ffn, mixer_norm, ffn_norm, post_mixer_norm=None, post_ffn_norm=None,
                  mixer_gate=None, ffn_gate=None):
@@ -115,6 +130,7 @@ class GatedPreNormResidualBlock:
         self.mixer, self.ffn = mixer, ffn
         self.mixer_norm, self.ffn_norm = mixer_norm, ffn_norm
         self.mixer_gate, self.ffn_gate = mixer_gate, ffn_gate
+        self._folded: bool | None = None      # whether the mixer forms its gate's product (decided at the first step)
 
     def parts(self) -> dict[str, object]:
         p = {"mixer": self.mixer, "mixer_norm": self.mixer_norm}
@@ -126,25 +142,51 @@ class GatedPreNormResidualBlock:
             p["ffn_gate"] = self.ffn_gate
         return p
 
+    def first_reader(self):
+        """(norm, reader) of the stream when this block starts; the reader is the block itself, so
+        only a block of this arrangement leaves the norm's result for it."""
+        return self.mixer_norm, self
+
+    def _next(self, env):
+        """The next block's first norm, if this block's last sum may leave its result."""
+        nxt = env.next_block_norm
+        if nxt is not None and isinstance(nxt[1], GatedPreNormResidualBlock):
+            return nxt[0]
+        return None
+
     def forward(self, x: torch.Tensor, batch, cache, env, pending=None):
         M, D = x.shape
         ws = env.workspace
         env.split_in = env.split_out = None
-        h = ws.get("block.h", (M, D), env.dtype)
-        self.mixer_norm.forward(h, x)
+        if self._folded is None:
+            self._folded = self.mixer_gate is not None and self.mixer_gate.give_rows_to(self.mixer)
+        if isinstance(pending, NormedRows) and pending.norm is self.mixer_norm and pending.values.shape == (M, D):
+            h = pending.values
+        else:
+            h = ws.get("block.h", (M, D), env.dtype)
+            self.mixer_norm.forward(h, x)
+        # the norm that reads x after each sum, and where its result goes (two buffers: h is still the gate's input)
+        after_mixer = self.ffn_norm if self.ffn is not None else self._next(env)
+        h2 = ws.get("block.h2" if h is ws.get("block.h", (M, D), env.dtype) else "block.h", (M, D), env.dtype)
+        left = None
         if self.mixer_gate is None:
             self.mixer.forward(h, x, True, batch, cache, env)
+            if self.ffn is not None:
+                self.ffn_norm.forward(h2, x)
         else:
             y = ws.get("block.t", (M, D), torch.float32)
             self.mixer.forward(h, y, False, batch, cache, env)
-            self.mixer_gate.add_gated(x, y, h, env)
+            z = self.mixer.extra_out if self._folded else None
+            self.mixer_gate.add_gated(x, y, h, env, z=z, next_norm=after_mixer, h_out=h2 if after_mixer is not None else None)
+            if self.ffn is None and after_mixer is not None:
+                left = NormedRows(h2, after_mixer)
         if self.ffn is None:
-            return None
-        self.ffn_norm.forward(h, x)
+            return left
+        after_ffn = self._next(env)
         if self.ffn_gate is None:
-            self.ffn.forward(h, x, True, batch, env)
-        else:
-            y = ws.get("block.t", (M, D), torch.float32)
-            self.ffn.forward(h, y, False, batch, env)
-            self.ffn_gate.add_gated(x, y, h, env)
-        return None
+            self.ffn.forward(h2, x, True, batch, env)
+            return None
+        y = ws.get("block.t", (M, D), torch.float32)
+        self.ffn.forward(h2, y, False, batch, env)
+        self.ffn_gate.add_gated(x, y, h2, env, next_norm=after_ffn, h_out=h if after_ffn is not None else None)
+        return NormedRows(h, after_ffn) if after_ffn is not None else None

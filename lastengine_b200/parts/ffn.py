@@ -58,8 +58,8 @@ class SwiGLU(FeedForward):
                 self.n_down: TensorSpec((self.D, self.F), MATRIX)}
 
     def load(self, tensors, env: BuildEnv) -> None:
-        # the products' fused epilogue is SwiGLU; other activations run as a kernel after the product
-        self.fused = (not env.is_float32) and self.F % 16 == 0 and self.act == kernels.SILU
+        self.fused = (not env.is_float32) and self.F % 16 == 0
+        self.epilogue = kernels.SWIGLU | (self.act << 8)      # the gated epilogue with this part's activation
         self.w13 = fuse_gate_up(tensors[self.n_gate], tensors[self.n_up], self.fused)
         self.w2 = tensors[self.n_down].contiguous()
 
@@ -72,7 +72,7 @@ class SwiGLU(FeedForward):
         scale, emit = env.take_split_in(), env.take_split_out()
         a = ws.get("ffn.a", (M, self.F), env.dtype)
         if self.fused:
-            kernels.linear(a, h, self.w13, kernels.SWIGLU, scale=scale)
+            kernels.linear(a, h, self.w13, self.epilogue, scale=scale)
         else:
             gu = ws.get("ffn.gu", (M, 2 * self.F), torch.float32)
             kernels.linear(gu, h, self.w13, scale=scale)

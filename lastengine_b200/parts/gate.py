@@ -32,9 +32,25 @@ class SigmoidGate(Part):
         self.w = tensors[self.tensor].contiguous()
         self.b = tensors[self.bias_tensor].to(torch.float32).contiguous() if self.bias else None
 
-    def add_gated(self, x: torch.Tensor, y: torch.Tensor, h: torch.Tensor, env: BuildEnv) -> None:
-        """x += y * sigmoid(R h + b); x the float residual, y the sublayer's float result, h its input."""
-        M = h.shape[0]
-        z = env.workspace.get("gate.z", (M, self.D), torch.float32)
-        kernels.linear(z, h, self.w)
-        kernels.gated_residual(x, y, z, self.b)
+    def add_gated(self, x: torch.Tensor, y: torch.Tensor, h: torch.Tensor, env: BuildEnv, z: torch.Tensor | None = None,
+                  next_norm=None, h_out: torch.Tensor | None = None) -> None:
+        """x += y * sigmoid(R h + b); x the float residual, y the sublayer's float result, h its input.
+        `z`: R h where another product has already formed it (a sublayer that took this gate's rows
+        into its own first product).  `next_norm` and `h_out`: the same launch also leaves the norm
+        of the new x there, for the sublayer that reads the stream next."""
+        if z is None:
+            M = h.shape[0]
+            z = env.workspace.get("gate.z", (M, self.D), torch.float32)
+            kernels.linear(z, h, self.w)
+        if next_norm is not None:
+            kernels.gated_residual(x, y, z, self.b, h_out, next_norm.weight, next_norm.eps)
+        else:
+            kernels.gated_residual(x, y, z, self.b)
+
+    def give_rows_to(self, part) -> bool:
+        """Lets `part` form R h in its own first product (one launch fewer); the gate then holds no matrix."""
+        take = getattr(part, "absorb_input_rows", None)
+        if self.w is None or take is None or not take(self.w):
+            return False
+        self.w = None
+        return True

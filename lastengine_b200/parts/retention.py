@@ -38,6 +38,7 @@ class RetentionMixer(Mixer):
         self.position = POSITION_ENCODINGS.get(pos.kind)(**pos.params)
         self.names = tuple(str(n) for n in names)
         self.w_in = self.w_out = self.decay = None
+        self.n_extra, self.extra_out = 0, None
 
     def tensors(self) -> dict[str, TensorSpec]:
         D, H, d, e = self.D, self.H, self.d, self.e
@@ -65,6 +66,15 @@ class RetentionMixer(Mixer):
         if self.rot > self.d:
             raise ValueError(f"{self.rot} rotated dimensions do not fit a head of {self.d}")
 
+    def absorb_input_rows(self, w: torch.Tensor) -> bool:
+        """Takes the rows of another product over the same input (a gate on this mixer's result) into
+        the fused projection; every forward then leaves their result in `extra_out` [rows, len(w)]."""
+        if w.dtype != self.w_in.dtype or w.shape[1] != self.D or self.n_extra:
+            return False
+        self.w_in = torch.cat([self.w_in, w], dim=0).contiguous()
+        self.n_extra = int(w.shape[0])
+        return True
+
     def flops_per_row(self) -> int:
         # the projections, and per head the state's update and its product with q
         return super().flops_per_row() + 4 * self.H * self.d * self.e
@@ -76,7 +86,9 @@ class RetentionMixer(Mixer):
         proj = ws.get("ret.proj", (M, self.w_in.shape[0]), env.dtype)
         kernels.linear(proj, h, self.w_in)
         q, k = proj[:, : H * d], proj[:, H * d: 2 * H * d]
-        v, g = proj[:, 2 * H * d: 2 * H * d + H * e], proj[:, 2 * H * d + H * e:]
+        v, g = proj[:, 2 * H * d: 2 * H * d + H * e], proj[:, 2 * H * d + H * e: 2 * H * (d + e)]
+        if self.n_extra:
+            self.extra_out = proj[:, 2 * H * (d + e):]
         o = ws.get("ret.o", (M, H * e), env.dtype)
         kernels.retention(o, q, k, v, g, cache.state, self.decay, self.inv_freq, self.rot, self.k_scale, self.eps,
                           batch, H, d, e)
