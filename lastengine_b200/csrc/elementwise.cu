@@ -294,12 +294,82 @@ __global__ void __launch_bounds__(256) gated_residual_kernel(
   for (int i = threadIdx.x; i < D; i += blockDim.x) hr[i] = from_f32<TH>(xr[i] * r * w[i]);   // a thread re-reads what it wrote
 }
 
+// The same with 16-byte accesses for rows of up to CH * 512 * 4 elements: a thread keeps its pieces of the
+// new row in registers between the sum and the norm, so a row is read once and a decode step's few
+// rows are not a chain of dependent loads.
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const bf16* p) {
+  const uint2 r = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
+  const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+  return make_float4(a.x, a.y, c.x, c.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(bf16* p, float4 v) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+}
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+template <typename TZ, typename TH, int CH>
+__global__ void __launch_bounds__(512) gated_residual_vec_kernel(
+    float* __restrict__ x, const float* __restrict__ y, const TZ* __restrict__ z, int ldz,
+    const float* __restrict__ b, TH* __restrict__ h, const float* __restrict__ w, float eps, int D) {
+  __shared__ float red[33];
+  pdl_trigger();
+  pdl_wait();
+  const size_t m = blockIdx.x;
+  const int n4 = D >> 2;
+  float4 v[CH];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < CH; c++) {
+    const int i = threadIdx.x + c * blockDim.x;
+    if (i < n4) {
+      const float4 xv = load4(x + m * D + 4 * i), yv = load4(y + m * D + 4 * i), zv = load4(z + m * ldz + 4 * i);
+      const float4 bv = b ? load4(b + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      v[c] = make_float4(xv.x + yv.x * sigmoid_f(zv.x + bv.x), xv.y + yv.y * sigmoid_f(zv.y + bv.y),
+                         xv.z + yv.z * sigmoid_f(zv.z + bv.z), xv.w + yv.w * sigmoid_f(zv.w + bv.w));
+      store4(x + m * D + 4 * i, v[c]);
+      ss += v[c].x * v[c].x + v[c].y * v[c].y + v[c].z * v[c].z + v[c].w * v[c].w;
+    }
+  }
+  if (!h) return;
+  ss = block_sum(ss, red);
+  const float r = 1.0f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+  for (int c = 0; c < CH; c++) {
+    const int i = threadIdx.x + c * blockDim.x;
+    if (i < n4) {
+      const float4 wv = load4(w + 4 * i);
+      store4(h + m * D + 4 * i, make_float4(v[c].x * r * wv.x, v[c].y * r * wv.y, v[c].z * r * wv.z, v[c].w * r * wv.w));
+    }
+  }
+}
+
+template <typename TZ, typename TH>
+static void launch_gated_residual(float* x, const float* y, const void* z, int ldz, const float* b, void* h, const float* w,
+                                  float eps, int M, int D, cudaStream_t st) {
+  const int n4 = D / 4;
+  const bool vec = D % 4 == 0 && n4 <= 4 * 512 && ldz % 4 == 0 && ((uintptr_t)z % (4 * sizeof(TZ))) == 0 &&
+                   ((uintptr_t)x % 16) == 0 && ((uintptr_t)y % 16) == 0 && (!b || ((uintptr_t)b % 16) == 0) &&
+                   (!h || (((uintptr_t)h % (4 * sizeof(TH))) == 0 && ((uintptr_t)w % 16) == 0));
+  if (vec) {
+    const int ch = n4 <= 512 ? 1 : (n4 <= 1024 ? 2 : 4);
+    const int threads = min(512, (ceil_div(n4, ch) + 31) / 32 * 32);
+    if (ch == 1) leb_launch(gated_residual_vec_kernel<TZ, TH, 1>, dim3(M), dim3(threads), 0, st, x, y, (const TZ*)z, ldz, b, (TH*)h, w, eps, D);
+    else if (ch == 2) leb_launch(gated_residual_vec_kernel<TZ, TH, 2>, dim3(M), dim3(threads), 0, st, x, y, (const TZ*)z, ldz, b, (TH*)h, w, eps, D);
+    else leb_launch(gated_residual_vec_kernel<TZ, TH, 4>, dim3(M), dim3(threads), 0, st, x, y, (const TZ*)z, ldz, b, (TH*)h, w, eps, D);
+    return;
+  }
+  leb_launch(gated_residual_kernel<TZ, TH>, dim3(M), dim3(D >= 1024 ? 256 : 128), 0, st, x, y, (const TZ*)z, ldz, b, (TH*)h, w, eps, D);
+}
+
 LEB_API int leb_gated_residual(float* x, const float* y, const void* z, int ldz, int z_dtype, const float* b, void* h,
                                int h_dtype, const float* w, float eps, int M, int D, cudaStream_t st) {
   if (M <= 0 || D <= 0) return 0;
   LEB_REQUIRE(!h || w, "leb_gated_residual: a norm needs its weight");
-  const dim3 grid(M), block(D >= 1024 ? 256 : 128);
-#define LEB_GR(TZ, TH) leb_launch(gated_residual_kernel<TZ, TH>, grid, block, 0, st, x, y, (const TZ*)z, ldz, b, (TH*)h, w, eps, D)
+#define LEB_GR(TZ, TH) launch_gated_residual<TZ, TH>(x, y, z, ldz, b, h, w, eps, M, D, st)
   if (z_dtype == LEB_F32 && (!h || h_dtype == LEB_F32)) LEB_GR(float, float);
   else if (z_dtype == LEB_F32 && h_dtype == LEB_BF16) LEB_GR(float, bf16);
   else if (z_dtype == LEB_BF16 && (!h || h_dtype == LEB_BF16)) LEB_GR(bf16, bf16);

@@ -279,13 +279,13 @@ def test_small_kernels_gated_activation_gated_sum_and_stream_addition():
     assert H.rel_err(xd, x.double() + x0.double() + 2 * vec.double()) < 1e-6
 
 
-@pytest.mark.parametrize("M,K,F", [(1, 64, 48), (8, 96, 160), (16, 256, 512), (40, 128, 256), (128, 256, 2048),
+@pytest.mark.parametrize("M,Kd,F", [(1, 64, 48), (8, 96, 160), (16, 256, 512), (40, 128, 256), (128, 256, 2048),
                                    (300, 64, 96), (700, 512, 1024), (1100, 256, 4096)])
-def test_gated_gelu_as_the_epilogue_of_every_bfloat16_product(M, K, F):
+def test_gated_gelu_as_the_epilogue_of_every_bfloat16_product(M, Kd, F):
     """Rows from one to over a thousand reach the weight stream, the sliced and the tiled tensor-core
     products and the one on pairs of SMs; each applies gelu(gate) * up before it stores."""
     from lastengine_b200.parts.ffn import fuse_gate_up
-    k = K_ = K
+    k = Kd
     g = torch.Generator().manual_seed(M)
     x = P.round_bf16(torch.randn(M, k, generator=g, dtype=torch.float64))
     wg = P.round_bf16(torch.randn(F, k, generator=g, dtype=torch.float64) * (2.0 / k ** 0.5))
