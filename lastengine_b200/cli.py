@@ -126,7 +126,10 @@ def cmd_inspect(a) -> int:
     print(f"architecture {architecture_name(raw)}: {len(plan.layers)} layers, hidden {plan.hidden_size}, "
           f"vocab {plan.vocab_size}")
     for i, l in enumerate(plan.layers):
-        print(f"  layer {i}: {l.mixer.kind} + {l.ffn.kind}")
+        print(f"  layer {i}: {l.mixer.kind} + {l.ffn.kind if l.ffn is not None else 'no feed-forward'}")
+    order = [e.layer for e in plan.schedule]
+    if order != list(range(len(plan.layers))):
+        print(f"  layers run in the order {' '.join(map(str, order))}")
     ck = open_checkpoint(a.path)
     by: dict[tuple[str, str], list[int]] = {}
     total = 0

@@ -120,3 +120,18 @@ def test_plain_rotation_keeps_norms_and_depends_on_distance_only():
     assert torch.equal(ra[..., 8:], a.repeat(3, 1, 1)[..., 8:])                  # the rest of the head passes unchanged
     assert torch.allclose((ra[0] * rb[0]).sum(), (ra[1] * rb[1]).sum(), atol=1e-9)
     assert torch.allclose(ra[2], P.rotate(a, torch.tensor([7]), 8, 100.0)[0])
+
+
+def test_command_line_writes_and_describes_a_folder(tmp_path, capsys):
+    import json
+    from lastengine_b200.cli import main
+    cfg = tmp_path / "c.json"
+    cfg.write_text(json.dumps(Z_A))
+    out = tmp_path / "model"
+    assert main(["init", "--config", str(cfg), "--seed", "5", "--out", str(out)]) == 0
+    capsys.readouterr()
+    assert main(["inspect", str(out)]) == 0
+    text = capsys.readouterr().out
+    assert "architecture Zekivik: 4 layers, hidden 64, vocab 200" in text
+    assert "layer 0: retention + gated_dense" in text and "layer 1: attention + no feed-forward" in text
+    assert "layers run in the order 0 1 2 1 2 3" in text
