@@ -29,7 +29,7 @@ __device__ __forceinline__ void store_value_tile(
     int t, const T* __restrict__ v_in, int kv_stride, CT* __restrict__ v_pool,
     const int* __restrict__ block_table, int bt_width, const int* __restrict__ row_seq,
     const int* __restrict__ row_pos, const int* __restrict__ seq_slot, int M, int nkv, int hd,
-    int page_size, int v_norm, float eps) {
+    int page_size, int v_norm, float eps, int vin) {      // hd: the head's width in the pool; vin <= hd: in v_in (the rest is stored as zeros)
   constexpr int LD = VT_DIMS + (sizeof(CT) == 2 ? 2 : 1);     // odd number of 32-bit words
   __shared__ CT tile[VT_ROWS * LD];
   __shared__ long long dst[VT_ROWS];                          // element offset of (row, dim 0), or -1
@@ -51,12 +51,12 @@ __device__ __forceinline__ void store_value_tile(
   for (int r = threadIdx.x >> 5; r < VT_ROWS; r += blockDim.x >> 5) {
     float ss = 0.f;
     if (v_norm && m0 + r < M)
-      for (int d = threadIdx.x & 31; d < hd; d += 32) {
-        float x = to_f32(v_in[(size_t)(m0 + r) * kv_stride + (size_t)kvh * hd + d]);
+      for (int d = threadIdx.x & 31; d < vin; d += 32) {
+        float x = to_f32(v_in[(size_t)(m0 + r) * kv_stride + (size_t)kvh * vin + d]);
         ss += x * x;
       }
     ss = warp_sum(ss);
-    if ((threadIdx.x & 31) == 0) rs[r] = v_norm ? 1.0f / sqrtf(ss / (float)hd + eps) : 1.f;
+    if ((threadIdx.x & 31) == 0) rs[r] = v_norm ? 1.0f / sqrtf(ss / (float)vin + eps) : 1.f;
   }
   for (int d0 = 0; d0 < hd; d0 += VT_DIMS) {
     int nd = min(VT_DIMS, hd - d0);
@@ -64,7 +64,9 @@ __device__ __forceinline__ void store_value_tile(
     for (int i = threadIdx.x; i < VT_ROWS * VT_DIMS; i += blockDim.x) {
       int r = i / VT_DIMS, d = i % VT_DIMS;
       if (d < nd && m0 + r < M)
-        tile[r * LD + d] = from_f32<CT>(to_f32(v_in[(size_t)(m0 + r) * kv_stride + (size_t)kvh * hd + d0 + d]) * rs[r]);
+        tile[r * LD + d] = d0 + d < vin
+            ? from_f32<CT>(to_f32(v_in[(size_t)(m0 + r) * kv_stride + (size_t)kvh * vin + d0 + d]) * rs[r])
+            : from_f32<CT>(0.f);
     }
     __syncthreads();
     for (int i = threadIdx.x; i < VT_ROWS * VT_DIMS; i += blockDim.x) {
@@ -85,7 +87,7 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_rope_store_kernel(
     const int* __restrict__ row_pos, const int* __restrict__ seq_slot,
     const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
     const float* __restrict__ inv_freq, int rope_dim, int neox, int M, int nh, int nkv, int hd,
-    int page_size, int vd, int v_norm) {
+    int page_size, int vd, int v_norm, int hin, int vin) {   // hin <= hd, vin <= vd: a head's width in q_in/k_in and v_in
   extern __shared__ float sm[];
   pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
@@ -93,7 +95,7 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_rope_store_kernel(
   if ((int)blockIdx.x >= M) {
     if (blockIdx.y == 0)
       store_value_tile<T, CT>(blockIdx.x - M, v_in, kv_stride, v_pool, block_table, bt_width, row_seq, row_pos,
-                              seq_slot, M, nkv, vd, page_size, v_norm, eps);
+                              seq_slot, M, nkv, vd, page_size, v_norm, eps, vin);
     return;
   }
   // ---- one row: q and k heads ----
@@ -122,20 +124,20 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_rope_store_kernel(
   if (head < total) {
     bool is_q = head < nh;
     if (!is_q && kdst < 0) return;  // padding rows and positions outside a window own no cache
-    const T* src = is_q ? q_in + (size_t)m * q_stride + (size_t)head * hd
-                        : k_in + (size_t)m * kv_stride + (size_t)(head - nh) * hd;
+    const T* src = is_q ? q_in + (size_t)m * q_stride + (size_t)head * hin
+                        : k_in + (size_t)m * kv_stride + (size_t)(head - nh) * hin;
     const float* nw = is_q ? q_norm_w : k_norm_w;
     float ss = 0.f;
     for (int i = lane; i < hd; i += 32) {
-      float x = to_f32(src[i]);
+      float x = i < hin ? to_f32(src[i]) : 0.f;      // a head stored wider than it is: zeros behind it
       v[i] = x;
       ss += x * x;
     }
     if (nw) {
       ss = warp_sum(ss);
-      float r = 1.0f / sqrtf(ss / (float)hd + eps);
+      float r = 1.0f / sqrtf(ss / (float)hin + eps);
       __syncwarp();
-      for (int i = lane; i < hd; i += 32) v[i] = v[i] * r * nw[i];
+      for (int i = lane; i < hin; i += 32) v[i] = v[i] * r * nw[i];
     }
     __syncwarp();
     if (inv_freq) {
@@ -170,14 +172,14 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_rope_store_lanes_kernel(
     const int* __restrict__ block_table, int bt_width,
     const int* __restrict__ row_seq, const int* __restrict__ row_pos, const int* __restrict__ seq_slot,
     const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
-    const float* __restrict__ inv_freq, int M, int nh, int nkv, int page_size, int per_warp, int vd, int v_norm) {
+    const float* __restrict__ inv_freq, int M, int nh, int nkv, int page_size, int per_warp, int vd, int v_norm, int vin) {
   constexpr int HD = EPL * 32, NP = EPL / 2, U = 4;
   pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
   if ((int)blockIdx.x >= M) {
     if (blockIdx.y == 0)
       store_value_tile<T, CT>(blockIdx.x - M, v_in, kv_stride, v_pool, block_table, bt_width, row_seq, row_pos,
-                              seq_slot, M, nkv, vd, page_size, v_norm, eps);
+                              seq_slot, M, nkv, vd, page_size, v_norm, eps, vin);
     return;
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -259,15 +261,18 @@ LEB_API int leb_qk_rope_store(void* q_out, const void* q_in, int q_stride, const
                               const int* row_pos, const int* seq_slot, const float* q_norm_w,
                               const float* k_norm_w, float eps, const float* inv_freq, int rope_dim,
                               int neox, int M, int nh, int nkv, int hd, int page_size, int vd, int v_norm,
-                              cudaStream_t st) {
+                              int hin, int vin, cudaStream_t st) {
   if (M <= 0) return 0;
   LEB_REQUIRE(hd >= 2 && hd <= 512, "leb_qk_rope_store: head_dim %d outside 2..512", hd);
   LEB_REQUIRE(rope_dim <= hd && rope_dim % 2 == 0, "leb_qk_rope_store: rope_dim %d does not fit head_dim %d", rope_dim, hd);
   if (vd <= 0) vd = hd;      // values as wide as keys
+  if (hin <= 0) hin = hd;    // heads come as wide as they are stored
+  if (vin <= 0) vin = vd;
+  LEB_REQUIRE(hin <= hd && vin <= vd && rope_dim <= hin, "leb_qk_rope_store: heads of %d/%d do not fit their stored width %d/%d", hin, vin, hd, vd);
   int tiles = k_in ? ceil_div(M, VT_ROWS) * nkv : 0;
   int total = nh + (k_in ? nkv : 0);
   dim3 block(32 * ROPE_WARPS);
-  if (dtype == LEB_BF16 && inv_freq && neox && rope_dim == hd && (hd == 64 || hd == 128)) {
+  if (dtype == LEB_BF16 && inv_freq && neox && rope_dim == hd && hin == hd && (hd == 64 || hd == 128)) {
     // heads per warp: one while the launch is small, up to all of a row's over 8 warps
     int per_warp = 1;
     const long long n_sm = sm_count();
@@ -277,12 +282,12 @@ LEB_API int leb_qk_rope_store(void* q_out, const void* q_in, int q_stride, const
       leb_launch(qk_rope_store_lanes_kernel<bf16, bf16, 2>, grid, block, 0, st,
           (bf16*)q_out, (const bf16*)q_in, q_stride, (const bf16*)k_in, (const bf16*)v_in, kv_stride,
           (bf16*)k_pool, (bf16*)v_pool, block_table, bt_width, row_seq, row_pos, seq_slot, q_norm_w,
-          k_norm_w, eps, inv_freq, M, nh, nkv, page_size, per_warp, vd, v_norm);
+          k_norm_w, eps, inv_freq, M, nh, nkv, page_size, per_warp, vd, v_norm, vin);
     else
       leb_launch(qk_rope_store_lanes_kernel<bf16, bf16, 4>, grid, block, 0, st,
           (bf16*)q_out, (const bf16*)q_in, q_stride, (const bf16*)k_in, (const bf16*)v_in, kv_stride,
           (bf16*)k_pool, (bf16*)v_pool, block_table, bt_width, row_seq, row_pos, seq_slot, q_norm_w,
-          k_norm_w, eps, inv_freq, M, nh, nkv, page_size, per_warp, vd, v_norm);
+          k_norm_w, eps, inv_freq, M, nh, nkv, page_size, per_warp, vd, v_norm, vin);
     LEB_CHECK_LAUNCH("leb_qk_rope_store");
     return 0;
   }
@@ -292,12 +297,12 @@ LEB_API int leb_qk_rope_store(void* q_out, const void* q_in, int q_stride, const
     leb_launch(qk_rope_store_kernel<float, float>, grid, block, smem, st,
         (float*)q_out, (const float*)q_in, q_stride, (const float*)k_in, (const float*)v_in,
         kv_stride, (float*)k_pool, (float*)v_pool, block_table, bt_width, row_seq, row_pos,
-        seq_slot, q_norm_w, k_norm_w, eps, inv_freq, rope_dim, neox, M, nh, nkv, hd, page_size, vd, v_norm);
+        seq_slot, q_norm_w, k_norm_w, eps, inv_freq, rope_dim, neox, M, nh, nkv, hd, page_size, vd, v_norm, hin, vin);
   else if (dtype == LEB_BF16)
     leb_launch(qk_rope_store_kernel<bf16, bf16>, grid, block, smem, st,
         (bf16*)q_out, (const bf16*)q_in, q_stride, (const bf16*)k_in, (const bf16*)v_in, kv_stride,
         (bf16*)k_pool, (bf16*)v_pool, block_table, bt_width, row_seq, row_pos, seq_slot, q_norm_w,
-        k_norm_w, eps, inv_freq, rope_dim, neox, M, nh, nkv, hd, page_size, vd, v_norm);
+        k_norm_w, eps, inv_freq, rope_dim, neox, M, nh, nkv, hd, page_size, vd, v_norm, hin, vin);
   else
     return leb_fail("leb_qk_rope_store: unknown dtype %d", dtype);
   LEB_CHECK_LAUNCH("leb_qk_rope_store");

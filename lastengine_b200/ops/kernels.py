@@ -98,7 +98,7 @@ def _declare(L) -> None:
         "leb_gather_rows": [P, P, I, P, I, I, I, P],
         "leb_add": [P, P, S, P],
         "leb_shortconv": [P, P, I, P, P, P, P, P, P, P, I, I, I, I, P],
-        "leb_qk_rope_store": [P, P, I, P, P, I, P, P, I, P, I, P, P, P, P, P, F, P, I, I, I, I, I, I, I, I, I, P],
+        "leb_qk_rope_store": [P, P, I, P, P, I, P, P, I, P, I, P, P, P, P, P, F, P, I, I, I, I, I, I, I, I, I, I, I, P],
         "leb_attention": [P, P, P, P, P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, I, P],
         "leb_gated_act": [P, I, P, I, I, I, I, P],
         "leb_gated_residual": [P, P, P, I, I, P, P, I, P, F, I, I, P],
@@ -447,24 +447,31 @@ def qk_rope_store(q_out: torch.Tensor, q_in: torch.Tensor, k_in: torch.Tensor | 
                   v_in: torch.Tensor | None, k_pool: torch.Tensor | None, v_pool: torch.Tensor | None,
                   block_table: torch.Tensor, batch, q_norm_w, k_norm_w, eps: float,
                   inv_freq: torch.Tensor | None, rope_dim: int, neox: bool, nh: int, nkv: int, hd: int,
-                  page_size: int, vd: int | None = None, v_norm: bool = False) -> None:
+                  page_size: int, vd: int | None = None, v_norm: bool = False, hd_in: int | None = None,
+                  vd_in: int | None = None) -> None:
     """Per-head norm and rotation of q and k; k and v go to the paged cache, q to q_out.
 
     q_in/k_in/v_in may be column slices of one fused projection (row stride = its width).
     `vd`: width of a value head where it is not the key head's; `v_norm`: every value head is
-    divided by its root mean square (with `eps`, no weight) before it is stored.
+    divided by its root mean square (with `eps`, no weight) before it is stored.  `hd_in` / `vd_in`:
+    width of a head in q_in/k_in and in v_in where heads are stored wider than they are (hd in q_out
+    and the key pool, vd in the value pool; the rest of a stored head is zeros, the norms run over the
+    head as it comes).
     """
     vd = hd if vd is None else int(vd)
+    hd_in = hd if hd_in is None else int(hd_in)
+    vd_in = vd if vd_in is None else int(vd_in)
+    assert hd_in <= hd and vd_in <= vd and q_out.shape[1] == nh * hd
     _cuda(q_out, "qk_rope_store.q_out")
     _cuda(q_in, "qk_rope_store.q_in", q_out.dtype, contiguous=False)
     M = q_out.shape[0]
-    assert q_in.stride(-1) == 1 and q_in.shape == (M, nh * hd)
+    assert q_in.stride(-1) == 1 and q_in.shape == (M, nh * hd_in)
     q_stride = q_in.stride(0)
     kv_stride = 0
     if k_in is not None:
         _cuda(k_in, "qk_rope_store.k_in", q_out.dtype, contiguous=False)
         _cuda(v_in, "qk_rope_store.v_in", q_out.dtype, contiguous=False)
-        assert k_in.shape == (M, nkv * hd) and v_in.shape == (M, nkv * vd)
+        assert k_in.shape == (M, nkv * hd_in) and v_in.shape == (M, nkv * vd_in)
         assert k_in.stride(0) == v_in.stride(0) and k_in.stride(-1) == 1 and v_in.stride(-1) == 1
         kv_stride = k_in.stride(0)
         _cuda(k_pool, "qk_rope_store.k_pool", q_out.dtype)
@@ -480,7 +487,8 @@ def qk_rope_store(q_out: torch.Tensor, q_in: torch.Tensor, k_in: torch.Tensor | 
         _ptr(q_out), _ptr(q_in), q_stride, _ptr(k_in), _ptr(v_in), kv_stride, _ptr(k_pool), _ptr(v_pool),
         _dt(q_out, "qk_rope_store"), _ptr(block_table), block_table.shape[1], _ptr(batch.row_seq),
         _ptr(batch.row_pos), _ptr(batch.seq_slot), _ptr(q_norm_w), _ptr(k_norm_w), float(eps),
-        _ptr(inv_freq), rope_dim, 1 if neox else 0, M, nh, nkv, hd, page_size, vd, 1 if v_norm else 0, _stream()))
+        _ptr(inv_freq), rope_dim, 1 if neox else 0, M, nh, nkv, hd, page_size, vd, 1 if v_norm else 0, hd_in, vd_in,
+        _stream()))
 
 
 _sm_counts: dict[int, int] = {}

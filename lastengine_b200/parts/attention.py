@@ -15,6 +15,12 @@ a weight (`qk_norm="unit"`); every value head divided by its root mean square be
 (`v_norm`).  The kernels norm before they rotate; a design that rotates first gets the same
 numbers, since a rotation of pairs leaves the head's sum of squares as it was.  `names` renames
 the tensors under the part's prefix.
+
+Key and value heads of different widths are cached at the wider of the two when that is a size the
+tensor-core attention kernels take: the narrower heads are stored with zeros behind them (a zero
+dimension changes no score and adds nothing to a value; the scale is explicit and the norms run over
+the head as it is), and the output projection gets zero columns where the padding is.  Other pairs
+of widths run the general kernel.
 """
 from __future__ import annotations
 
@@ -47,6 +53,9 @@ class AttentionMixer(Mixer):
         self.vd = self.hd if v_head_dim is None else int(v_head_dim)
         if self.vd > 256:
             raise ValueError(f"v_head_dim {self.vd} is larger than the attention kernels take (256)")
+        # widths in the cache: the wider of the two where the fast kernels take it
+        wide = max(self.hd, self.vd)
+        self.khd, self.kvd = (wide, wide) if self.hd != self.vd and wide in (32, 64, 96, 128) else (self.hd, self.vd)
         self.taps = int(conv_taps)
         if not 0 <= self.taps <= 16:
             raise ValueError(f"conv_taps {conv_taps}: 0 (no convolution) or 1..16")
@@ -88,7 +97,7 @@ class AttentionMixer(Mixer):
         return t
 
     def cache_spec(self):
-        kv = KVSpec(self.nkv, self.hd, self.window, None if self.vd == self.hd else self.vd)
+        kv = KVSpec(self.nkv, self.khd, self.window, None if self.kvd == self.khd else self.kvd)
         if self.taps <= 1:       # a single tap looks at the current row only
             return kv
         # the convolution's memory: the last taps-1 projected values of every q, k and v channel
@@ -103,6 +112,10 @@ class AttentionMixer(Mixer):
             parts.append(tensors[n["gate"]])
         self.w_in = torch.cat(parts, dim=0).contiguous() if len(parts) > 1 else parts[0].contiguous()
         self.w_out = tensors[n["o"]].contiguous()
+        if self.kvd != self.vd:      # zero columns where the cached value heads are wider than the heads
+            w = torch.zeros((self.D, self.nh, self.kvd), dtype=self.w_out.dtype, device=self.w_out.device)
+            w[:, :, : self.vd] = self.w_out.view(self.D, self.nh, self.vd)
+            self.w_out = w.view(self.D, self.nh * self.kvd).contiguous()
         if self.qk_norm:
             self.q_norm_w = tensors[n["q_norm"]].contiguous()
             self.k_norm_w = tensors[n["k_norm"]].contiguous() if self.own_kv else None
@@ -127,7 +140,7 @@ class AttentionMixer(Mixer):
         return True
 
     def flops_per_query_key(self) -> int:
-        return 2 * self.nh * (self.hd + self.vd)    # a score and a weighted value, a multiply-add each, per head and dimension
+        return 2 * self.nh * (self.khd + self.kvd)    # a score and a weighted value, a multiply-add each, per head and dimension
 
     def forward(self, h, out, accumulate, batch, cache, env) -> None:
         nh, nkv, hd, vd = self.nh, self.nkv, self.hd, self.vd
@@ -163,19 +176,20 @@ class AttentionMixer(Mixer):
             kernels.causal_conv(conv, proj[:, :col], self.w_conv, cache.state, batch)
             q_in, k_in = conv[:, : nh * hd], conv[:, nh * hd: (nh + nkv) * hd]
             v_in = conv[:, (nh + nkv) * hd:]
-        q = ws.get("attn.q", (M, nh * hd), env.dtype)
+        khd, kvd = self.khd, self.kvd
+        q = ws.get("attn.q", (M, nh * khd), env.dtype)
         kp, vp = (cache.k, cache.v) if writes else (None, None)
         rotary = self.position.fused_rotary()
         raw = None
-        if (rotary is not None and plain_v
+        if (rotary is not None and plain_v and khd == hd
                 and kernels.decode_attention_takes_raw(env.dtype, batch, M, nh, nkv, hd, cache.page_size, *rotary)):
             # a decode step: the attention kernel norms and rotates q and k and stores k and v itself
             raw = kernels.RawQKV(q_in, k_in, v_in, self.q_norm_w, self.k_norm_w if writes else None, self.eps, *rotary)
         elif rotary is not None:
             # per-head norm, rotation and the cache write in one launch
             kernels.qk_rope_store(q, q_in, k_in, v_in, kp, vp, cache.block_table, batch, self.q_norm_w,
-                                  self.k_norm_w if writes else None, self.eps, *rotary, nh, nkv, hd, cache.page_size,
-                                  vd=vd, v_norm=self.v_norm)
+                                  self.k_norm_w if writes else None, self.eps, *rotary, nh, nkv, khd, cache.page_size,
+                                  vd=kvd, v_norm=self.v_norm, hd_in=hd, vd_in=vd)
         elif not plain_v:
             raise NotImplementedError("value heads of their own width or norm with a position encoding that is no rotation")
         else:
@@ -194,13 +208,13 @@ class AttentionMixer(Mixer):
             self.position.apply(qn.view(M, nh, hd), kn.view(M, nkv, hd) if writes else None, batch.row_pos)
             kernels.qk_rope_store(q, qn, kn, vn, kp, vp, cache.block_table, batch, None, None, self.eps,
                                   None, 0, True, nh, nkv, hd, cache.page_size)
-        o = ws.get("attn.o", (M, nh * vd), env.dtype)
-        n_splits = kernels.attention_splits(batch, nkv, nh // nkv, hd=hd)
+        o = ws.get("attn.o", (M, nh * kvd), env.dtype)
+        n_splits = kernels.attention_splits(batch, nkv, nh // nkv, hd=khd)
         scratch = None
         if n_splits > 1:
-            scratch = ws.get("attn.part", (M * nh * n_splits * (max(hd, vd) + 2),), torch.float32)
-        kernels.attention(o, None if raw is not None else q, cache.k, cache.v, cache.block_table, batch, nh, nkv, hd,
+            scratch = ws.get("attn.part", (M * nh * n_splits * (max(khd, kvd) + 2),), torch.float32)
+        kernels.attention(o, None if raw is not None else q, cache.k, cache.v, cache.block_table, batch, nh, nkv, khd,
                           cache.page_size, self.window, self.scale, gate=gate, n_splits=n_splits, scratch=scratch, raw=raw,
-                          vd=vd)
+                          vd=kvd)
         kernels.linear(out, o, self.w_out, kernels.ACCUMULATE if accumulate else kernels.STORE,
                        emit=emit if accumulate else None)

@@ -146,6 +146,8 @@ ATT_CASES = [  # heads, kv, dim, vdim, taps, scale, rot dims
     (4, 1, 128, 128, 1, 0.09, 32),
     (5, 5, 24, 40, 4, 0.25, 0),
     (2, 2, 96, 32, 2, 0.1, 48),
+    (6, 2, 64, 32, 3, 0.15, 64),       # cached 64 wide: the tensor-core kernels with zero-padded values
+    (2, 2, 32, 128, 2, 0.2, 16),       # cached 128 wide: zero-padded queries and keys
 ]
 
 

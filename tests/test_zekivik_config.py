@@ -37,7 +37,9 @@ def test_plan_schedule_cache_entries_and_stream_additions():
     specs = m.cache_specs()
     assert len(specs) == 6                                   # every run of a layer has its own entry
     assert specs[0] == StateSpec((2, 16, 24), torch.float32)
-    assert specs[1] == specs[3] == (KVSpec(2, 32, 0, 16), StateSpec((4 * 32 + 2 * 32 + 2 * 16, 2), torch.float32))
+    # key heads of 32 and value heads of 16 are cached 32 wide (a size the tensor-core kernels take); 16 and 48 stay
+    assert specs[1] == specs[3] == (KVSpec(2, 32, 0, None), StateSpec((4 * 32 + 2 * 32 + 2 * 16, 2), torch.float32))
+    assert specs[5][0] == KVSpec(1, 16, 0, 48)
     names = set(m.tensor_specs())
     assert {"embed.weight", "head.weight", "final.norm.weight", "loop.step", "l0.norm1.weight", "l0.norm2.weight",
             "l0.rg1", "l0.rg1.b", "l0.rg2", "l0.rg2.b", "l0.mix.q", "l0.mix.g", "l0.mlp.gate", "l1.mix.q.conv",
