@@ -360,7 +360,9 @@ def compare_designs(which: str, steps: int, warmup: int) -> int:
             eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=8 * 2304 + 4096, max_seqs=16)
             nums = model_numbers(eng)
             r = {"weights_gb": round(nums["weight_bytes"] / 1e9, 3)}
+            print(f"[bench] {size_name} {label}: {r['weights_gb']} GB of weights", file=sys.stderr, flush=True)
             pre_ms = time_prefill(eng, PREFILL_TOKENS, 3, 5, rng)
+            print(f"[bench] {size_name} {label}: prompt of {PREFILL_TOKENS} tokens {pre_ms:.3f} ms", file=sys.stderr, flush=True)
             flops = (PREFILL_TOKENS * nums["linear_flops_per_token"] + nums["head_flops_per_row"]
                      + nums["attn_flops_per_qk"] * PREFILL_TOKENS * (PREFILL_TOKENS + 1) // 2)
             r["prefill_2048_ms"] = pre_ms
@@ -372,6 +374,7 @@ def compare_designs(which: str, steps: int, warmup: int) -> int:
                 r[f"decode_b{b}_tok_s"] = d["tok_s"]
                 r[f"decode_b{b}_launches"] = d["launches_per_step"]
                 r[f"decode_b{b}_frac_of_hbm"] = decode_step_bytes(eng, nums, b, d["avg_context"]) / (d["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"]
+                print(f"[bench] {size_name} {label}: decode b{b} {d['ms_per_step']:.4f} ms/step", file=sys.stderr, flush=True)
             # every entry point of a prompt and of a decode step, one after the other under the event timer
             toks = rng.integers(0, eng.vocab_size, size=PREFILL_TOKENS).tolist()
             s = eng.new_sequence()

@@ -47,6 +47,13 @@ static inline cudaError_t leb_launch(void (*kern)(KArgs...), dim3 grid, dim3 blo
   cfg.numAttrs = g_leb_pdl ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
+// Launches of a scope without programmatic dependent launch (strictly after their predecessor).
+struct LebPlainLaunches {
+  int saved;
+  bool off;
+  explicit LebPlainLaunches(bool turn_off) : saved(g_leb_pdl), off(turn_off) { if (off) g_leb_pdl = 0; }
+  ~LebPlainLaunches() { if (off) g_leb_pdl = saved; }
+};
 // silu(g) * u.  The bfloat16 products' epilogues take 2^x and the reciprocal from the special
 // function unit (relative error about 1e-6, far below the rounding of the bfloat16 they store):
 // with exact expf and division an epilogue of a few warps is bound by its instructions.

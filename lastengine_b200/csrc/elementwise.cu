@@ -369,6 +369,10 @@ LEB_API int leb_gated_residual(float* x, const float* y, const void* z, int ldz,
                                int h_dtype, const float* w, float eps, int M, int D, cudaStream_t st) {
   if (M <= 0 || D <= 0) return 0;
   LEB_REQUIRE(!h || w, "leb_gated_residual: a norm needs its weight");
+  // Launched strictly after its predecessor: with programmatic dependent launch a prompt step of several
+  // thousand rows (a block per row here) now and then never finished on B200 -- one sequence of 8 x 2,000
+  // rows in fifteen, never with these two kernels launched plainly; what waits on what was not found.
+  LebPlainLaunches plain(true);
 #define LEB_GR(TZ, TH) launch_gated_residual<TZ, TH>(x, y, z, ldz, b, h, w, eps, M, D, st)
   if (z_dtype == LEB_F32 && (!h || h_dtype == LEB_F32)) LEB_GR(float, float);
   else if (z_dtype == LEB_F32 && h_dtype == LEB_BF16) LEB_GR(float, bf16);
@@ -397,6 +401,10 @@ __global__ void stream_add_kernel(float* __restrict__ x, const float* __restrict
 LEB_API int leb_stream_add(float* x, const float* x0, const float* vec, int M, int D, cudaStream_t st) {
   size_t total = (size_t)M * D;
   if (total == 0 || (!x0 && !vec)) return 0;
+  // Launched strictly after its predecessor: with programmatic dependent launch a prompt step of several
+  // thousand rows (a block per row here) now and then never finished on B200 -- one sequence of 8 x 2,000
+  // rows in fifteen, never with these two kernels launched plainly; what waits on what was not found.
+  LebPlainLaunches plain(true);
   leb_launch(stream_add_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, x, x0, vec, D, total);
   LEB_CHECK_LAUNCH("leb_stream_add");
   return 0;
