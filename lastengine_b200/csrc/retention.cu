@@ -242,8 +242,10 @@ __global__ void __launch_bounds__(RCT) retention_chunk_state_kernel(
   __syncthreads();
   float* out = scratch + ((size_t)(base + c) * H + h) * d * e;
   const int te = e8 / 8, tiles = (d8 / 8) * te;
+  // a thread's eight columns are two groups of four, half a row apart: neighbouring threads then read
+  // neighbouring 16 bytes of shared memory
   for (int t = threadIdx.x; t < tiles; t += blockDim.x) {
-    const int r0 = (t / te) * 8, c0 = (t % te) * 8;
+    const int r0 = (t / te) * 8, ca = (t % te) * 4, cb = e8 / 2 + ca;
     float acc[8][8];
 #pragma unroll
     for (int a = 0; a < 8; a++)
@@ -251,7 +253,7 @@ __global__ void __launch_bounds__(RCT) retention_chunk_state_kernel(
       for (int bb = 0; bb < 8; bb++) acc[a][bb] = 0.f;
     for (int j = 0; j < nrows; j++) {
       const float4 k0 = *reinterpret_cast<const float4*>(ks + j * d8 + r0), k1 = *reinterpret_cast<const float4*>(ks + j * d8 + r0 + 4);
-      const float4 v0 = *reinterpret_cast<const float4*>(vs + j * e8 + c0), v1 = *reinterpret_cast<const float4*>(vs + j * e8 + c0 + 4);
+      const float4 v0 = *reinterpret_cast<const float4*>(vs + j * e8 + ca), v1 = *reinterpret_cast<const float4*>(vs + j * e8 + cb);
       const float kk[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
       const float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
 #pragma unroll
@@ -262,8 +264,10 @@ __global__ void __launch_bounds__(RCT) retention_chunk_state_kernel(
 #pragma unroll
     for (int a = 0; a < 8; a++)
 #pragma unroll
-      for (int bb = 0; bb < 8; bb++)
-        if (r0 + a < d && c0 + bb < e) out[(size_t)(r0 + a) * e + c0 + bb] = acc[a][bb];
+      for (int bb = 0; bb < 8; bb++) {
+        const int cc = bb < 4 ? ca + bb : cb + bb - 4;
+        if (r0 + a < d && cc < e) out[(size_t)(r0 + a) * e + cc] = acc[a][bb];
+      }
   }
 }
 
@@ -376,9 +380,9 @@ __global__ void __launch_bounds__(RCT) retention_chunk_out_kernel(
   for (int u = 0; u < 2; u++) {
     const int t = threadIdx.x + u * RCT;
     if (t >= tiles) break;
-    const int i0 = (t / te) * 4, c0 = (t % te) * 8;
+    const int i0 = (t / te) * 4, ca = (t % te) * 4, cb = e8 / 2 + ca;      // columns as in the state kernel
     for (int j = 0; j < min(nrows, i0 + 4); j++) {
-      const float4 v0 = *reinterpret_cast<const float4*>(vs + j * e8 + c0), v1 = *reinterpret_cast<const float4*>(vs + j * e8 + c0 + 4);
+      const float4 v0 = *reinterpret_cast<const float4*>(vs + j * e8 + ca), v1 = *reinterpret_cast<const float4*>(vs + j * e8 + cb);
       const float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
 #pragma unroll
       for (int a = 0; a < 4; a++) {
@@ -393,18 +397,27 @@ __global__ void __launch_bounds__(RCT) retention_chunk_out_kernel(
   for (int r0 = 0; r0 < d; r0 += slab) {
     const int nr = min(slab, d - r0);
     __syncthreads();
-    for (int idx = threadIdx.x; idx < nr * e8; idx += blockDim.x) {
-      const int r = idx / e8, cc = idx - r * e8;
-      ks[idx] = cc < e ? Sg[(size_t)(r0 + r) * e + cc] : 0.f;
+    if ((e & 3) == 0) {          // 16-byte pieces of the state's rows
+      const int q4 = e8 / 4;
+      for (int idx = threadIdx.x; idx < nr * q4; idx += blockDim.x) {
+        const int r = idx / q4, c4 = idx - r * q4;
+        reinterpret_cast<float4*>(ks)[idx] = 4 * c4 < e ? *reinterpret_cast<const float4*>(Sg + (size_t)(r0 + r) * e + 4 * c4)
+                                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < nr * e8; idx += blockDim.x) {
+        const int r = idx / e8, cc = idx - r * e8;
+        ks[idx] = cc < e ? Sg[(size_t)(r0 + r) * e + cc] : 0.f;
+      }
     }
     __syncthreads();
 #pragma unroll
     for (int u = 0; u < 2; u++) {
       const int t = threadIdx.x + u * RCT;
       if (t >= tiles) break;
-      const int i0 = (t / te) * 4, c0 = (t % te) * 8;
+      const int i0 = (t / te) * 4, ca = (t % te) * 4, cb = e8 / 2 + ca;
       for (int r = 0; r < nr; r++) {
-        const float4 s0 = *reinterpret_cast<const float4*>(ks + r * e8 + c0), s1 = *reinterpret_cast<const float4*>(ks + r * e8 + c0 + 4);
+        const float4 s0 = *reinterpret_cast<const float4*>(ks + r * e8 + ca), s1 = *reinterpret_cast<const float4*>(ks + r * e8 + cb);
         const float ss[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
         for (int a = 0; a < 4; a++) {
@@ -420,11 +433,11 @@ __global__ void __launch_bounds__(RCT) retention_chunk_out_kernel(
   for (int u = 0; u < 2; u++) {
     const int t = threadIdx.x + u * RCT;
     if (t >= tiles) break;
-    const int i0 = (t / te) * 4, c0 = (t % te) * 8;
+    const int i0 = (t / te) * 4, ca = (t % te) * 4, cb = e8 / 2 + ca;
 #pragma unroll
     for (int a = 0; a < 4; a++)
 #pragma unroll
-      for (int bb = 0; bb < 8; bb++) vs[(i0 + a) * e8 + c0 + bb] = acc[u][a][bb];
+      for (int bb = 0; bb < 8; bb++) vs[(i0 + a) * e8 + (bb < 4 ? ca + bb : cb + bb - 4)] = acc[u][a][bb];
   }
   __syncthreads();
   // per row: the head's root mean square, the gate, the store
