@@ -58,7 +58,7 @@ class SwiGLU(FeedForward):
                 self.n_down: TensorSpec((self.D, self.F), MATRIX)}
 
     def load(self, tensors, env: BuildEnv) -> None:
-        self.fused = (not env.is_float32) and self.F % 16 == 0
+        self.fused = (not env.is_float32) and self.F % 16 == 0 and self.D % 8 == 0
         self.epilogue = kernels.SWIGLU | (self.act << 8)      # the gated epilogue with this part's activation
         self.w13 = fuse_gate_up(tensors[self.n_gate], tensors[self.n_up], self.fused)
         self.w2 = tensors[self.n_down].contiguous()

@@ -2,7 +2,7 @@
 constant: width, vocabulary, eps, layer order, which layers have a feed-forward, head counts and
 grouping, key and value head sizes (equal, smaller, larger, not multiples of 32), taps (1 to 5),
 scale, rotated part of the head (none, part, all), decays (0, 1 and between), and the loop (none,
-inside the stack, over all of it, a single pass)."""
+inside the stack, over all of it, a single pass); one has no size that is a multiple of 8."""
 
 
 def att(heads, kv_heads, dim, vdim, conv, scale, rot_dims, base):
@@ -59,4 +59,13 @@ Z_D = {
     "loop": {"start": 1, "stop": 2, "times": 1},
 }
 
-ALL = {"A": Z_A, "B": Z_B, "C": Z_C, "D": Z_D}
+# no size a multiple of 8: the plain bfloat16 product and the scalar forms of the row kernels
+Z_E = {
+    "architecture": "Zekivik", "vocab": 101, "width": 36, "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "attention", "mixer": att(3, 1, 20, 12, 3, 0.22, 10, 3000.0), "mlp": dense(50)},
+        {"type": "retention", "mixer": ret(1, 14, 18, [0.93], 6, 900.0), "mlp": None},
+    ],
+}
+
+ALL = {"A": Z_A, "B": Z_B, "C": Z_C, "D": Z_D, "E": Z_E}
