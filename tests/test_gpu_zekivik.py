@@ -431,3 +431,24 @@ def test_greedy_generation_through_the_entry_point(name, dtype, graphs, dirs):
     assert compared >= steps * len(prompts) // 3
     assert eng.cache.slots.n_held == 0
     eng.cache.check()
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "bfloat16")])
+def test_a_sequence_written_out_and_read_back_goes_on_where_it_stood(name, dtype, dirs):
+    """Keys, values, the convolution's memory and the retention state of every layer run go out as bytes
+    and come back into other slots and pages."""
+    from lastengine_b200 import Engine
+    eng = Engine.from_pretrained(dirs[name], dtype=dtype, max_tokens=512, max_seqs=4)
+    r = reqs_for(name, [90], 44)[0]
+    s = eng.new_sequence()
+    eng.step([s], [r[:70]], None)
+    data = eng.export_sequence(s)
+    a = H.to_host(eng.step([s], [r[70:]], [list(range(20))]))
+    other = eng.new_sequence()                       # the copy lands in another slot and other pages
+    eng.step([other], [r[:5]], None)
+    t = eng.import_sequence(data)
+    assert t != s and eng.length(t) == 70
+    b = H.to_host(eng.step([t], [r[70:]], [list(range(20))]))
+    eng.release([s, other, t])
+    assert H.rel_err(b, a) < 1e-6
+    eng.cache.check()
