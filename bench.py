@@ -24,6 +24,9 @@ A step is one decode step of the whole batch.  One JSON line goes to stdout:
              runs) against the bytes or flops it has to move
 
 Weights (1.8 GB) are far larger than L2, so consecutive steps cannot be served from L2.
+
+`--compare zekivik` leaves all of that aside and prints a line of its own: prompt and decode times of the
+Zekivik design at a few layer sizes beside the LFM3 hybrid at equal sizes, with every kernel entry point's time.
 """
 from __future__ import annotations
 
