@@ -434,10 +434,10 @@ def main() -> int:
     ap.add_argument("--only-prefill", action="store_true", help="time the prompt step only (for profiling)")
     ap.add_argument("--only-decode", action="store_true", help="skip the prompt timing (for profiling)")
     ap.add_argument("--unequal", type=int, default=0, metavar="N",
-                    help="instead of the contract's run: N requests with prompts of U[64, 2048] tokens generate "
+                    help="instead of the default run: N requests with prompts of U[64, 2048] tokens generate "
                          "--steps tokens each in one batch through the Python entry point (prints its own JSON line)")
     ap.add_argument("--compare", default="", choices=["", "zekivik"],
-                    help="instead of the contract's run: prefill and decode of that design at a few layer sizes beside "
+                    help="instead of the default run: prefill and decode of that design at a few layer sizes beside "
                          "the LFM3 hybrid at equal sizes, with every kernel's time (prints its own JSON line)")
     args = ap.parse_args()
 
