@@ -452,3 +452,43 @@ def test_a_sequence_written_out_and_read_back_goes_on_where_it_stood(name, dtype
     eng.release([s, other, t])
     assert H.rel_err(b, a) < 1e-6
     eng.cache.check()
+
+
+def test_replay_program_with_a_cache_sized_to_the_tokens_alone(dirs, tmp_path):
+    """bin/trace_run with --max-tokens equal to the tokens the live requests hold, not rounded up to pages:
+    three unequal requests start together (the shortest with one token), go on token by token and leave one
+    by one; every request's last page is partly filled."""
+    import json
+    import subprocess
+    import sys
+    name = "A"
+    reqs = dict(zip("xyz", reqs_for(name, [12, 75, 3], 45)))
+    first = {"x": 9, "y": 70, "z": 1}
+    steps = [{"step": 0, "entries": [{"id": r, "tokens": reqs[r][:first[r]], "want": list(range(first[r]))} for r in "xyz"],
+              "end": []}]
+    fed, live, n = dict(first), ["x", "y", "z"], 1
+    while live:
+        ent = [{"id": r, "tokens": [reqs[r][fed[r]]], "want": [0]} for r in live]
+        for r in live:
+            fed[r] += 1
+        ended = [r for r in live if fed[r] >= len(reqs[r])]
+        steps.append({"step": n, "entries": ent, "end": ended})
+        live = [r for r in live if r not in ended]
+        n += 1
+    out = str(tmp_path / "out")
+    p = subprocess.run([sys.executable, os.path.join(H.ROOT, "bin", "trace_run"), "--model", dirs[name], "--dtype", "float32",
+                        "--out", out, "--max-tokens", str(sum(len(t) for t in reqs.values()))],
+                       input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=900)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(n)]
+    V = ALL[name]["vocab"]
+    got = {r: [] for r in reqs}
+    for st in steps:
+        lg = torch.from_numpy(np.fromfile(os.path.join(out, f"{st['step']}.f32"), dtype="<f4").reshape(-1, V))
+        at = 0
+        for e in st["entries"]:
+            got[e["id"]].append(lg[at:at + len(e["want"])])
+            at += len(e["want"])
+        assert at == lg.shape[0]
+    for r, t in reqs.items():
+        assert H.rel_err(torch.cat(got[r]), plain(name, dirs, t, False)) < H.TOL_F32, r
