@@ -85,6 +85,7 @@ def zekivik_plan(cfg: ZekivikConfig) -> ModelPlan:
         names={"embedding": "embed", "final_norm": "final.norm", "head": "head"},
         tensor_aliases=_alias, checkpoint_names=_checkpoint_name,
         stream_adds=tuple(adds), stream_tables=tables,
+        unused_tensors=() if adds else (LOOP_TABLE,),      # a checkpoint may carry the table of a loop over no layers
         # the model keeps its signal through the looped passes with weights of this size
         init_std=0.05, init_stds={".conv": 0.5, LOOP_TABLE: 0.3})
 

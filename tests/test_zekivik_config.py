@@ -137,3 +137,18 @@ def test_command_line_writes_and_describes_a_folder(tmp_path, capsys):
     assert "architecture Zekivik: 4 layers, hidden 64, vocab 200" in text
     assert "layer 0: retention + gated_dense" in text and "layer 1: attention + no feed-forward" in text
     assert "layers run in the order 0 1 2 1 2 3" in text
+
+
+def test_a_loop_over_no_layers_is_no_loop_and_its_table_is_passed_by(tmp_path):
+    import json
+    from lastengine_b200.weights import write_model_dir
+    from lastengine_b200.weights.loader import check_names
+    from lastengine_b200.engine.model import Model
+    from lastengine_b200.parts.base import BuildEnv
+    cfg = copy.deepcopy(Z_D)
+    cfg["loop"] = {"start": 2, "stop": 2, "times": 3}
+    plan = plan_of(cfg)
+    assert [e.layer for e in plan.schedule] == [0, 1, 2] and not plan.stream_adds
+    assert "loop.step" in plan.unused_tensors
+    m = Model(plan, BuildEnv(device=torch.device("cpu"), dtype=torch.float32))
+    assert "loop.step" not in m.tensor_specs()
