@@ -289,16 +289,23 @@ __global__ void __launch_bounds__(256) retention_chunk_scan_kernel(
   for (int j = 0; j < RC; j++) gl *= g;
   float* sp = slot >= 0 ? state + ((size_t)slot * H + h) * de + x : nullptr;
   float S = sp ? *sp : 0.f;
-  for (int c = 0; c < nc; c++) {
-    float* u = scratch + ((size_t)(base + c) * H + h) * de + x;
-    const float U = *u;
-    *u = S;
-    float gp = gl;
-    if (c == nc - 1 && n - c * RC < RC) {
-      gp = 1.f;
-      for (int j = 0; j < n - c * RC; j++) gp *= g;
+  const size_t step = (size_t)H * de;                       // from one chunk's element to the next chunk's
+  float* u0 = scratch + ((size_t)base * H + h) * de + x;
+  const int last = n - (nc - 1) * RC;                       // rows of the last chunk
+  float glast = 1.f;
+  for (int j = 0; j < last; j++) glast *= g;
+  // eight chunks' sums are asked for before any is used: the loads do not depend on the running state
+  for (int c0 = 0; c0 < nc; c0 += 8) {
+    float U[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) U[j] = c0 + j < nc ? u0[(size_t)(c0 + j) * step] : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      if (c0 + j < nc) {
+        u0[(size_t)(c0 + j) * step] = S;
+        S = (c0 + j == nc - 1 ? glast : gl) * S + U[j];
+      }
     }
-    S = gp * S + U;
   }
   if (sp) *sp = S;
 }
