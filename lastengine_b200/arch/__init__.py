@@ -1,2 +1,2 @@
 """Architectures the library knows.  Importing registers them."""
-from . import lfm3, zekivik  # noqa: F401
+from . import lenesun, lfm3, zekivik  # noqa: F401

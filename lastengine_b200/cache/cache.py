@@ -8,6 +8,9 @@ reused.  Layers are grouped by what they need:
   `[entry, page, kv_head, value_dim, position in page]`, with a page pool and a page list per
   sequence of its own.  A windowed group gives pages back once every position in
   them has left the window.
+* a latent group per distinct (rank, rotated key width) is a KV group with one "head" whose key row is
+  the cached row `[latent | rotated key part]` and whose value pool is empty (the values are read out
+  of the same row); pages, tables, export and import are those of any KV group.
 * a state group per distinct (shape, dtype): `[entry, slot, *shape]`, zeroed when a slot is
   given out (the reference zeroes its convolution state on reset, src/gpu/dense.rs:264-267).
 
@@ -24,7 +27,7 @@ from dataclasses import dataclass
 import numpy as np
 import torch
 
-from ..parts.base import KVSpec, StateSpec
+from ..parts.base import KVSpec, LatentSpec, StateSpec
 from .allocator import CacheError, CacheFull, IdPool
 
 PAGE_SIZE = 64
@@ -124,12 +127,12 @@ class Cache:
                 continue
             several = list(spec) if isinstance(spec, (tuple, list)) else [spec]
             kinds = [type(s) for s in several]
-            if kinds.count(KVSpec) > 1 or kinds.count(StateSpec) > 1:
+            if kinds.count(KVSpec) + kinds.count(LatentSpec) > 1 or kinds.count(StateSpec) > 1:
                 raise TypeError(f"cache entry {entry}: at most one KVSpec and one StateSpec per entry, got {spec!r}")
             for s in several:
                 by_spec.setdefault(s, []).append(entry)
         for spec, entries in by_spec.items():
-            if isinstance(spec, KVSpec):
+            if isinstance(spec, (KVSpec, LatentSpec)):
                 self.kv_groups.append(KVGroup(spec, entries, self.n_pages, page_size, dtype, device))
                 for e in entries:
                     self._where.setdefault(e, []).append(("kv", len(self.kv_groups) - 1))

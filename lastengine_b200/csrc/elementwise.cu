@@ -26,7 +26,7 @@ LEB_API long long leb_launch_count() { return g_leb_launches; }
 // x[m, :] = table[tokens[m], :]            (reference: src/dense.rs:172-177 takes the row as is)
 template <typename T>
 __global__ void embed_kernel(float* __restrict__ x, const T* __restrict__ table,
-                             const int* __restrict__ tokens, int D, int V) {
+                             const int* __restrict__ tokens, int D, int V, float scale) {
   pdl_trigger();   // the kernel after this one may start and wait (see common.cuh)
   pdl_wait();
   int m = blockIdx.x;
@@ -34,17 +34,17 @@ __global__ void embed_kernel(float* __restrict__ x, const T* __restrict__ table,
   tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);  // ids are validated on the host; never read outside
   const T* row = table + (size_t)tok * D;
   float* o = x + (size_t)m * D;
-  for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = to_f32(row[i]);
+  for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = to_f32(row[i]) * scale;   // scale 1 leaves the row as it is
 }
 
 LEB_API int leb_embed(float* x, const void* table, int table_dtype, const int* tokens, int M, int D,
-                      int V, cudaStream_t st) {
+                      int V, float scale, cudaStream_t st) {
   if (M <= 0) return 0;
   int threads = D >= 1024 ? 256 : 128;
   if (table_dtype == LEB_F32)
-    leb_launch(embed_kernel<float>, dim3(M), dim3(threads), 0, st, x, (const float*)table, tokens, D, V);
+    leb_launch(embed_kernel<float>, dim3(M), dim3(threads), 0, st, x, (const float*)table, tokens, D, V, scale);
   else if (table_dtype == LEB_BF16)
-    leb_launch(embed_kernel<bf16>, dim3(M), dim3(threads), 0, st, x, (const bf16*)table, tokens, D, V);
+    leb_launch(embed_kernel<bf16>, dim3(M), dim3(threads), 0, st, x, (const bf16*)table, tokens, D, V, scale);
   else
     return leb_fail("leb_embed: unknown table dtype %d", table_dtype);
   LEB_CHECK_LAUNCH("leb_embed");
@@ -227,12 +227,13 @@ LEB_API int leb_add(float* x, const float* y, size_t n, cudaStream_t st) {
 
 // ---------------------------------------------------------------------------------------------
 // a[m, j] = act(gu[m, j]) * gu[m, F + j] with act chosen by code: 0 silu, 1 the tanh form of gelu,
-// gelu(z) = z/2 * (1 + tanh(sqrt(2/pi) * (z + 0.044715 z^3))).
+// gelu(z) = z/2 * (1 + tanh(sqrt(2/pi) * (z + 0.044715 z^3))), 2 the clamped sigmoid form (below).
 __device__ __forceinline__ float gelu_tanh_f(float z) {
   return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 template <typename TI, typename TO>
-__global__ void gated_act_kernel(TO* __restrict__ a, const TI* __restrict__ gu, int F, size_t total, int act) {
+__global__ void gated_act_kernel(TO* __restrict__ a, const TI* __restrict__ gu, int F, size_t total, int act,
+                                 float limit, float alpha) {
   pdl_trigger();
   pdl_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -241,22 +242,30 @@ __global__ void gated_act_kernel(TO* __restrict__ a, const TI* __restrict__ gu, 
   int j = (int)(i - m * F);
   float g = to_f32(gu[m * 2 * F + j]);
   float u = to_f32(gu[m * 2 * F + F + j]);
-  float r = act == 1 ? gelu_tanh_f(g) * u : g / (1.0f + expf(-g)) * u;
+  float r;
+  if (act == 2) {        // clamped: g' = min(g, limit), u' = clamp(u, -limit, limit); g' sigmoid(alpha g') (u' + 1)
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    r = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+  } else {
+    r = act == 1 ? gelu_tanh_f(g) * u : g / (1.0f + expf(-g)) * u;
+  }
   a[i] = from_f32<TO>(r);
 }
 
 LEB_API int leb_gated_act(void* a, int out_dtype, const void* gu, int in_dtype, int M, int F, int act,
-                          cudaStream_t st) {
+                          float limit, float alpha, cudaStream_t st) {
   size_t total = (size_t)M * F;
   if (total == 0) return 0;
-  LEB_REQUIRE(act == 0 || act == 1, "leb_gated_act: unknown activation %d", act);
+  LEB_REQUIRE(act >= 0 && act <= 2, "leb_gated_act: unknown activation %d", act);
+  LEB_REQUIRE(act != 2 || limit > 0.f, "leb_gated_act: the clamped activation needs a positive limit");
   dim3 grid((unsigned)((total + 255) / 256)), block(256);
   if (in_dtype == LEB_F32 && out_dtype == LEB_F32)
-    leb_launch(gated_act_kernel<float, float>, grid, block, 0, st, (float*)a, (const float*)gu, F, total, act);
+    leb_launch(gated_act_kernel<float, float>, grid, block, 0, st, (float*)a, (const float*)gu, F, total, act, limit, alpha);
   else if (in_dtype == LEB_F32 && out_dtype == LEB_BF16)
-    leb_launch(gated_act_kernel<float, bf16>, grid, block, 0, st, (bf16*)a, (const float*)gu, F, total, act);
+    leb_launch(gated_act_kernel<float, bf16>, grid, block, 0, st, (bf16*)a, (const float*)gu, F, total, act, limit, alpha);
   else if (in_dtype == LEB_BF16 && out_dtype == LEB_BF16)
-    leb_launch(gated_act_kernel<bf16, bf16>, grid, block, 0, st, (bf16*)a, (const bf16*)gu, F, total, act);
+    leb_launch(gated_act_kernel<bf16, bf16>, grid, block, 0, st, (bf16*)a, (const bf16*)gu, F, total, act, limit, alpha);
   else
     return leb_fail("leb_gated_act: unsupported dtypes in=%d out=%d", in_dtype, out_dtype);
   LEB_CHECK_LAUNCH("leb_gated_act");
@@ -407,5 +416,77 @@ LEB_API int leb_stream_add(float* x, const float* x0, const float* vec, int M, i
   LebPlainLaunches plain(true);
   leb_launch(stream_add_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, x, x0, vec, D, total);
   LEB_CHECK_LAUNCH("leb_stream_add");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Layer norm with a weight and no bias: y = (x - mean) / sqrt(var + eps) * w, var the mean of the
+// squared deviations (two passes over the row: the mean first, then the deviations).  All float.
+//   rows != null : input row m is x[rows[m]]
+template <typename TO>
+__device__ __forceinline__ void layernorm_row(TO* __restrict__ o, const float* __restrict__ xi,
+                                              const float* __restrict__ w, int D, float eps, float* red) {
+  float s = 0.f;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) s += xi[i];
+  const float mean = block_sum(s, red) / (float)D;
+  float v = 0.f;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    const float d = xi[i] - mean;
+    v += d * d;
+  }
+  const float r = 1.0f / sqrtf(block_sum(v, red) / (float)D + eps);
+  for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = from_f32<TO>((xi[i] - mean) * r * w[i]);
+}
+
+template <typename TO>
+__global__ void layernorm_kernel(TO* __restrict__ out, const float* __restrict__ x, const float* __restrict__ w,
+                                 const int* __restrict__ rows, int D, float eps) {
+  __shared__ float red[33];
+  pdl_wait();
+  const int m = blockIdx.x;
+  layernorm_row(out + (size_t)m * D, x + (size_t)(rows ? rows[m] : m) * D, w, D, eps, red);
+}
+
+LEB_API int leb_layernorm(void* out, int out_dtype, const float* x, const float* w, const int* rows, int M, int D,
+                          float eps, cudaStream_t st) {
+  if (M <= 0) return 0;
+  LebPlainLaunches plain(true);
+  const int threads = D >= 2048 ? 512 : (D >= 512 ? 256 : 128);
+  if (out_dtype == LEB_F32) leb_launch(layernorm_kernel<float>, dim3(M), dim3(threads), 0, st, (float*)out, x, w, rows, D, eps);
+  else if (out_dtype == LEB_BF16) leb_launch(layernorm_kernel<bf16>, dim3(M), dim3(threads), 0, st, (bf16*)out, x, w, rows, D, eps);
+  else return leb_fail("leb_layernorm: unknown output dtype %d", out_dtype);
+  LEB_CHECK_LAUNCH("leb_layernorm");
+  return 0;
+}
+
+// The sum of a layer whose sublayers read one norm: x[m, :] += mult * y[m, :] (y holds the sum of
+// the sublayers' results), and with `h` the layer norm of the new row for whatever reads the
+// stream next.  A thread re-reads only what it wrote.
+template <typename TH>
+__global__ void scaled_residual_kernel(float* __restrict__ x, const float* __restrict__ y, float mult,
+                                       TH* __restrict__ h, const float* __restrict__ w, float eps, int D) {
+  __shared__ float red[33];
+  pdl_wait();
+  const size_t m = blockIdx.x;
+  float* xr = x + m * D;
+  const float* yr = y + m * D;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) xr[i] = xr[i] + mult * yr[i];
+  if (!h) return;
+  layernorm_row(h + m * D, xr, w, D, eps, red);
+}
+
+LEB_API int leb_scaled_residual(float* x, const float* y, float mult, void* h, int h_dtype, const float* w, float eps,
+                                int M, int D, cudaStream_t st) {
+  if (M <= 0 || D <= 0) return 0;
+  LEB_REQUIRE(!h || w, "leb_scaled_residual: a norm needs its weight");
+  LebPlainLaunches plain(true);
+  const int threads = D >= 2048 ? 512 : (D >= 512 ? 256 : 128);
+  if (!h || h_dtype == LEB_F32)
+    leb_launch(scaled_residual_kernel<float>, dim3(M), dim3(threads), 0, st, x, y, mult, (float*)h, w, eps, D);
+  else if (h_dtype == LEB_BF16)
+    leb_launch(scaled_residual_kernel<bf16>, dim3(M), dim3(threads), 0, st, x, y, mult, (bf16*)h, w, eps, D);
+  else
+    return leb_fail("leb_scaled_residual: unknown dtype %d", h_dtype);
+  LEB_CHECK_LAUNCH("leb_scaled_residual");
   return 0;
 }

@@ -6,14 +6,29 @@
 // Router of this architecture: z = Wr . h (float), s = sigmoid(z), selection score c = s + bias
 // (the bias chooses, it does not weigh), I = the k largest c with ties to the lower index (the
 // reference's router breaks ties the same way, src/cuda/kernels.cu:450), weight_e = s_e, divided
-// by the sum of the chosen s when norm_topk is set, times the scaling factor.
+// by the sum of the chosen s when norm_topk is set, times the scaling factor.  A second router
+// (softmax over the chosen logits, the bias inside the logit) is selected by the same argument.
 #include "common.cuh"
 
 #define MOE_MAX_E 256
 #define MOE_MAX_K 16
 
+// The softmax router (mode ROUTER_SOFTMAX_CHOSEN in the place of norm_topk): logits z + bias, the bias
+// part of the logit; the k largest are chosen and weighted by the softmax over the chosen logits alone.
+#define ROUTER_SOFTMAX_CHOSEN 2
+__device__ __forceinline__ void router_score(float* s, float* c, float z, float b, int mode) {
+  if (mode == ROUTER_SOFTMAX_CHOSEN) {
+    *s = *c = z + b;
+  } else {
+    const float sg = 1.0f / (1.0f + expf(-z));
+    *s = sg;
+    *c = sg + b;
+  }
+}
+
 // One row's choice by one warp: the k largest selection scores c, ties to the lower index; the
-// weights are the sigmoids sg of the chosen, divided by their sum when norm_topk is set, times scaling.
+// weights are the sigmoids sg of the chosen, divided by their sum when norm_topk is set, times scaling
+// (softmax router: e^(logit - largest chosen logit) over the sum of these, times scaling).
 __device__ __forceinline__ void router_choose(int* __restrict__ ids, float* __restrict__ wts, const float* c,
                                               const float* sg, int E, int k, int norm_topk, float scaling, int lane) {
   unsigned taken = 0;   // bit j: this lane's candidate lane + 32 j is chosen already
@@ -34,11 +49,11 @@ __device__ __forceinline__ void router_choose(int* __restrict__ ids, float* __re
     }
     if ((be & 31) == lane) taken |= 1u << (be >> 5);
     chosen[j] = be;
-    sum += sg[be];
+    sum += norm_topk == ROUTER_SOFTMAX_CHOSEN ? expf(sg[be] - sg[chosen[0]]) : sg[be];   // chosen[0] holds the largest logit
   }
   if (lane == 0) {
     for (int j = 0; j < k; j++) {
-      float w = sg[chosen[j]];
+      float w = norm_topk == ROUTER_SOFTMAX_CHOSEN ? expf(sg[chosen[j]] - sg[chosen[0]]) : sg[chosen[j]];
       if (norm_topk) w = w / sum;
       ids[j] = chosen[j];
       wts[j] = w * scaling;
@@ -108,11 +123,7 @@ moe_router_kernel(int* __restrict__ topk_ids, float* __restrict__ topk_w, const 
 #pragma unroll
     for (int r = 0; r < R; r++) {
       const float zz = warp_sum(z[r]);
-      if (lane == 0) {
-        const float sg = 1.0f / (1.0f + expf(-zz));
-        s_[r * E + e] = sg;
-        c_[r * E + e] = sg + (bias ? bias[e] : 0.f);
-      }
+      if (lane == 0) router_score(s_ + r * E + e, c_ + r * E + e, zz, bias ? bias[e] : 0.f, norm_topk);
     }
   }
   __syncthreads();
@@ -204,11 +215,7 @@ moe_router_rows_kernel(int* __restrict__ topk_ids, float* __restrict__ topk_w, c
 #pragma unroll
       for (int r = 0; r < RB; r++) {
         const float zz = warp_sum(z[q][r]);
-        if (lane == 0 && on[q]) {
-          const float sg = 1.0f / (1.0f + expf(-zz));
-          s_[r * E + e] = sg;
-          c_[r * E + e] = sg + (bias ? bias[e] : 0.f);
-        }
+        if (lane == 0 && on[q]) router_score(s_ + r * E + e, c_ + r * E + e, zz, bias ? bias[e] : 0.f, norm_topk);
       }
     }
   }

@@ -29,7 +29,7 @@ class Model:
             gates = {role: GATES.get(g.kind)(**g.params) for role, g in ls.gates.items()}
             self.blocks.append(BLOCKS.get(ls.block)(
                 mixer=mixer, ffn=ffn, mixer_norm=norm(ls.mixer_norm), ffn_norm=norm(ls.ffn_norm),
-                post_mixer_norm=norm(ls.post_mixer_norm), post_ffn_norm=norm(ls.post_ffn_norm), **gates))
+                post_mixer_norm=norm(ls.post_mixer_norm), post_ffn_norm=norm(ls.post_ffn_norm), **gates, **ls.block_params))
         self.hidden_size, self.vocab_size = plan.hidden_size, plan.vocab_size
         # additions to the residual stream between schedule entries, and the tables they take rows from
         self.stream_adds: dict[int, list] = {}

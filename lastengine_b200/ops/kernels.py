@@ -92,7 +92,7 @@ class KernelTimer:
 def _declare(L) -> None:
     P, I, F, S = c_void_p, c_int, c_float, c_size_t
     sig = {
-        "leb_embed": [P, P, I, P, I, I, I, P],
+        "leb_embed": [P, P, I, P, I, I, I, F, P],
         "leb_rmsnorm": [P, I, P, P, P, I, I, F, I, P],
         "leb_swiglu": [P, I, P, I, I, I, P],
         "leb_gather_rows": [P, P, I, P, I, I, I, P],
@@ -100,7 +100,13 @@ def _declare(L) -> None:
         "leb_shortconv": [P, P, I, P, P, P, P, P, P, P, I, I, I, I, P],
         "leb_qk_rope_store": [P, P, I, P, P, I, P, P, I, P, I, P, P, P, P, P, F, P, I, I, I, I, I, I, I, I, I, I, I, P],
         "leb_attention": [P, P, P, P, P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, I, P],
-        "leb_gated_act": [P, I, P, I, I, I, I, P],
+        "leb_gated_act": [P, I, P, I, I, I, I, F, F, P],
+        "leb_layernorm": [P, I, P, P, P, I, I, F, P],
+        "leb_scaled_residual": [P, P, F, P, I, P, F, I, I, P],
+        "leb_latent_prep": [P, P, I, I, P, P, I, P, P, P, P, P, F, P, I, I, I, I, I, I, P],
+        "leb_latent_q_split": [P, P, P, I, P, P, I, I, I, I, I, I, P],
+        "leb_heads_to_rows": [P, P, I, I, I, I, P],
+        "leb_latent_attention": [P, I, P, P, P, P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
         "leb_gemm_bf16_any": [P, I, P, P, I, I, I, I, I, I, P],
         "leb_gated_residual": [P, P, P, I, I, P, P, I, P, F, I, I, P],
         "leb_stream_add": [P, P, P, I, I, P],
@@ -206,15 +212,15 @@ def _dt(t: torch.Tensor, name: str) -> int:
 
 
 # ----------------------------------------------------------------------------------------------
-def embed(x: torch.Tensor, table: torch.Tensor, tokens: torch.Tensor) -> None:
-    """x[m] = table[tokens[m]] as float."""
+def embed(x: torch.Tensor, table: torch.Tensor, tokens: torch.Tensor, scale: float = 1.0) -> None:
+    """x[m] = table[tokens[m]] * scale as float."""
     _cuda(x, "embed.x", torch.float32)
     _cuda(table, "embed.table")
     _cuda(tokens, "embed.tokens", torch.int32)
     M, D = x.shape
     V = table.shape[0]
     assert table.shape[1] == D and tokens.numel() >= M
-    _check(lib().leb_embed(_ptr(x), _ptr(table), _dt(table, "embed.table"), _ptr(tokens), M, D, V, _stream()))
+    _check(lib().leb_embed(_ptr(x), _ptr(table), _dt(table, "embed.table"), _ptr(tokens), M, D, V, float(scale), _stream()))
 
 
 def rmsnorm(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, eps: float,
@@ -234,6 +240,37 @@ def rmsnorm(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, eps: float,
                              float(eps), 1 if add else 0, _stream()))
 
 
+def layernorm(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, eps: float, rows: torch.Tensor | None = None) -> None:
+    """out = (x - mean) / sqrt(var + eps) * w per row (no bias); x is float."""
+    _cuda(out, "layernorm.out")
+    _cuda(x, "layernorm.x", torch.float32)
+    _cuda(w, "layernorm.w", torch.float32)
+    M, D = out.shape
+    assert x.shape[1] == D and w.numel() == D
+    if rows is not None:
+        _cuda(rows, "layernorm.rows", torch.int32)
+        assert rows.numel() >= M
+    else:
+        assert x.shape[0] >= M
+    _check(lib().leb_layernorm(_ptr(out), _dt(out, "layernorm.out"), _ptr(x), _ptr(w), _ptr(rows), M, D, float(eps), _stream()))
+
+
+def scaled_residual(x: torch.Tensor, y: torch.Tensor, mult: float, h: torch.Tensor | None = None,
+                    norm_w: torch.Tensor | None = None, eps: float = 0.0) -> None:
+    """x += mult * y (both float [M, D]); with `h` [M, D] the launch also leaves there the layer norm
+    (weight `norm_w`, no bias) of the new rows."""
+    _cuda(x, "scaled_residual.x", torch.float32)
+    _cuda(y, "scaled_residual.y", torch.float32)
+    M, D = x.shape
+    assert y.shape == (M, D)
+    if h is not None:
+        _cuda(h, "scaled_residual.h")
+        _cuda(norm_w, "scaled_residual.norm_w", torch.float32)
+        assert h.shape == (M, D) and norm_w.numel() == D
+    _check(lib().leb_scaled_residual(_ptr(x), _ptr(y), float(mult), _ptr(h), _dt(h, "scaled_residual.h") if h is not None else F32,
+                                     _ptr(norm_w), float(eps), M, D, _stream()))
+
+
 def swiglu(out: torch.Tensor, gu: torch.Tensor) -> None:
     """out[m, j] = silu(gu[m, j]) * gu[m, F + j]."""
     _cuda(out, "swiglu.out")
@@ -243,17 +280,18 @@ def swiglu(out: torch.Tensor, gu: torch.Tensor) -> None:
     _check(lib().leb_swiglu(_ptr(out), _dt(out, "swiglu.out"), _ptr(gu), _dt(gu, "swiglu.gu"), M, Fd, _stream()))
 
 
-SILU, GELU_TANH = 0, 1      # activations of a gated feed-forward
+SILU, GELU_TANH, CLAMPED_SIGMOID = 0, 1, 2      # activations of a gated feed-forward
 
 
-def gated_act(out: torch.Tensor, gu: torch.Tensor, act: int) -> None:
-    """out[m, j] = act(gu[m, j]) * gu[m, F + j], act SILU or GELU_TANH."""
+def gated_act(out: torch.Tensor, gu: torch.Tensor, act: int, limit: float = 0.0, alpha: float = 1.0) -> None:
+    """out[m, j] = act(gu[m, j]) * gu[m, F + j], act SILU or GELU_TANH; or CLAMPED_SIGMOID: with
+    g = min(gu[m, j], limit) and u = clamp(gu[m, F + j], -limit, limit), g * sigmoid(alpha * g) * (u + 1)."""
     _cuda(out, "gated_act.out")
     _cuda(gu, "gated_act.gu")
     M, Fd = out.shape
     assert gu.shape == (M, 2 * Fd)
     _check(lib().leb_gated_act(_ptr(out), _dt(out, "gated_act.out"), _ptr(gu), _dt(gu, "gated_act.gu"), M, Fd,
-                               int(act), _stream()))
+                               int(act), float(limit), float(alpha), _stream()))
 
 
 def gated_residual(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor, bias: torch.Tensor | None,
@@ -493,6 +531,90 @@ def qk_rope_store(q_out: torch.Tensor, q_in: torch.Tensor, k_in: torch.Tensor | 
 
 
 _sm_counts: dict[int, int] = {}
+
+
+def latent_prep(cq: torch.Tensor, proj: torch.Tensor, pool: torch.Tensor | None, block_table, batch,
+                q_norm_w: torch.Tensor, kv_norm_w: torch.Tensor | None, eps: float, inv_freq: torch.Tensor | None,
+                rot_dims: int, rank: int, rot: int, page_size: int) -> None:
+    """The rows of a step of a latent-attention layer after the down projections: proj [M, q_rank
+    (+ rank + rot)] -> cq [M, q_rank] = rmsnorm(proj[:, :q_rank]) * q_norm_w, and with `pool`
+    [page, page_size, rank + rot] the cache row [rmsnorm(latent) * kv_norm_w | rotated key part] at every
+    row's position (pairs (2i, 2i+1) of the first rot_dims dimensions turned by pos * inv_freq[i])."""
+    _cuda(cq, "latent_prep.cq")
+    _cuda(proj, "latent_prep.proj", cq.dtype, contiguous=False)
+    _cuda(q_norm_w, "latent_prep.q_norm_w", torch.float32)
+    M, q_rank = cq.shape
+    assert proj.shape[0] == M and proj.stride(1) == 1 and q_norm_w.numel() == q_rank
+    if pool is not None:
+        _cuda(pool, "latent_prep.pool", cq.dtype)
+        _cuda(kv_norm_w, "latent_prep.kv_norm_w", torch.float32)
+        assert proj.shape[1] == q_rank + rank + rot and kv_norm_w.numel() == rank
+        assert pool.shape[-1] == rank + rot and pool.shape[-2] == page_size
+    if rot_dims:
+        _cuda(inv_freq, "latent_prep.inv_freq", torch.float32)
+        assert inv_freq.numel() == rot_dims // 2
+    _check(lib().leb_latent_prep(_ptr(cq), _ptr(proj), proj.stride(0), _dt(cq, "latent_prep.cq"), _ptr(pool),
+                                 _ptr(block_table), block_table.shape[1] if block_table is not None else 0,
+                                 _ptr(batch.row_seq), _ptr(batch.row_pos), _ptr(batch.seq_slot), _ptr(q_norm_w),
+                                 _ptr(kv_norm_w), float(eps), _ptr(inv_freq) if rot_dims else None, int(rot_dims), M, q_rank,
+                                 int(rank), int(rot), int(page_size), _stream()))
+
+
+def latent_q_split(qn: torch.Tensor, qr: torch.Tensor, q: torch.Tensor, row_pos: torch.Tensor,
+                   inv_freq: torch.Tensor | None, rot_dims: int, H: int, dim: int, rot: int) -> None:
+    """q [M, H * (dim + rot)] -> qn [H, M, dim_p] (each head's first `dim` numbers, head-major, zeros
+    behind them) and qr [M, H, rot] (each head's last `rot` numbers, rotated by the row's position)."""
+    _cuda(q, "latent_q_split.q")
+    _cuda(qn, "latent_q_split.qn", q.dtype)
+    _cuda(qr, "latent_q_split.qr", q.dtype)
+    M = q.shape[0]
+    dim_p = qn.shape[2]
+    assert q.shape[1] == H * (dim + rot) and qn.shape[:2] == (H, M) and dim_p >= dim and qr.numel() == M * H * rot
+    _check(lib().leb_latent_q_split(_ptr(qn), _ptr(qr), _ptr(q), _dt(q, "latent_q_split.q"), _ptr(row_pos),
+                                    _ptr(inv_freq) if rot_dims else None, int(rot_dims), M, H, dim, dim_p, rot, _stream()))
+
+
+def heads_to_rows(out: torch.Tensor, src: torch.Tensor) -> None:
+    """src [H, M, w] -> out [M, H * w]."""
+    _cuda(out, "heads_to_rows.out")
+    _cuda(src, "heads_to_rows.src", out.dtype)
+    H, M, w = src.shape
+    assert out.shape == (M, H * w)
+    _check(lib().leb_heads_to_rows(_ptr(out), _ptr(src), _dt(out, "heads_to_rows.out"), M, H, w, _stream()))
+
+
+def latent_attention_splits(batch, H: int) -> int:
+    """Pieces the key range of a decode step is cut into so that the blocks fill the SMs (1 for prompts)."""
+    if batch.max_qlen != 1:
+        return 1
+    blocks = batch.n_seqs * -(-H // 8)
+    tiles = -(-batch.max_kvlen // 32)
+    want = max(1, (2 * sm_count()) // max(1, blocks))
+    return int(max(1, min(want, tiles // 4, 64)))
+
+
+def latent_attention(out: torch.Tensor, qt: torch.Tensor, qr: torch.Tensor, pool: torch.Tensor, block_table, batch,
+                     sink: torch.Tensor | None, rank: int, rot: int, page_size: int, scale: float,
+                     n_splits: int = 1, scratch: torch.Tensor | None = None) -> None:
+    """Causal attention of every row over its sequence's cached rows [c | k^r] (pool [page, page_size,
+    rank + rot]): query vectors qt [H, M, rank] and qr [M, H, rot]; scores scale * ([qt | qr] . [c | k^r]);
+    softmax with `sink` [H] as one more logit without a value; out [H, M, >= rank] = sum p c."""
+    _cuda(out, "latent_attention.out")
+    _cuda(qt, "latent_attention.qt", out.dtype)
+    _cuda(qr, "latent_attention.qr", out.dtype)
+    _cuda(pool, "latent_attention.pool", out.dtype)
+    H, M, ld = out.shape
+    assert qt.shape == (H, M, rank) and qr.numel() == M * H * rot and pool.shape[-1] == rank + rot and ld >= rank
+    if sink is not None:
+        _cuda(sink, "latent_attention.sink", torch.float32)
+        assert sink.numel() == H
+    if n_splits > 1:
+        _cuda(scratch, "latent_attention.scratch", torch.float32)
+        assert scratch.numel() >= M * H * n_splits * (rank + 2)
+    _check(lib().leb_latent_attention(_ptr(out), ld, _ptr(scratch), _ptr(qt), _ptr(qr), _ptr(pool), _dt(out, "latent_attention.out"),
+                                      _ptr(block_table), block_table.shape[1], _ptr(batch.seq_slot), _ptr(batch.seq_pos0),
+                                      _ptr(batch.seq_qstart), _ptr(batch.seq_qlen), _ptr(sink), M, batch.n_seqs, H, int(rank),
+                                      int(rot), int(page_size), float(scale), batch.max_qlen, int(n_splits), _stream()))
 
 
 def sm_count() -> int:
@@ -846,7 +968,10 @@ _OPTIONAL_TC: list = [None]
 
 # ----------------------------------------------------------------------------------------------
 def moe_router(topk_ids: torch.Tensor, topk_w: torch.Tensor, h: torch.Tensor, wr: torch.Tensor,
-               bias: torch.Tensor | None, norm_topk: bool, scaling: float) -> None:
+               bias: torch.Tensor | None, norm_topk: bool, scaling: float, softmax_chosen: bool = False) -> None:
+    """The k experts of every row and their weights.  Default: sigmoid scores, the bias only chooses,
+    weights are the chosen sigmoids (over their sum with norm_topk).  `softmax_chosen`: logits Wr h + bias,
+    the k largest chosen, weights the softmax over the chosen logits alone."""
     _cuda(topk_ids, "moe_router.topk_ids", torch.int32)
     _cuda(topk_w, "moe_router.topk_w", torch.float32)
     _cuda(h, "moe_router.h")
@@ -858,7 +983,7 @@ def moe_router(topk_ids: torch.Tensor, topk_w: torch.Tensor, h: torch.Tensor, wr
         _cuda(bias, "moe_router.bias", torch.float32)
         assert bias.numel() == E
     _check(lib().leb_moe_router(_ptr(topk_ids), _ptr(topk_w), _ptr(h), _dt(h, "moe_router.h"), _ptr(wr),
-                                _ptr(bias), M, D, E, k, 1 if norm_topk else 0, float(scaling), _stream()))
+                                _ptr(bias), M, D, E, k, 2 if softmax_chosen else (1 if norm_topk else 0), float(scaling), _stream()))
 
 
 def moe_align(offsets: torch.Tensor, sorted_pair: torch.Tensor, pair_row: torch.Tensor,

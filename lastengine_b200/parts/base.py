@@ -13,8 +13,8 @@ Every part:
     load(tensors, env)                             takes its tensors (already on the device,
                                                    in the dtype of their role) and may fuse them
 Mixer:
-    cache_spec() -> KVSpec | StateSpec | None      what it keeps per sequence (or a tuple of one
-                    | (KVSpec, StateSpec)           KVSpec and one StateSpec for a mixer that keeps both)
+    cache_spec() -> KVSpec | LatentSpec | StateSpec what it keeps per sequence (or a tuple of one
+                    | (KVSpec, StateSpec) | None    KVSpec and one StateSpec for a mixer that keeps both)
     forward(h, out, accumulate, batch, cache, env) h: [rows, hidden] normed input in the
                                                    activation dtype; writes (or adds) its
                                                    result into the float tensor `out`
@@ -71,6 +71,24 @@ class KVSpec:
 
 
 @dataclass(frozen=True)
+class LatentSpec:
+    """One row per position that stands for every head's key and value: a latent vector of `rank`
+    numbers followed by `rope_dim` numbers of a rotated key part shared by all heads.  Paged like keys
+    and values (one pool of rows `[position][rank + rope_dim]`, nothing stored apart for the values)."""
+    rank: int
+    rope_dim: int
+
+    # how the cache's page groups see it: one "head" whose key row is the whole cached row
+    n_kv_heads = 1
+    window = 0
+    value_dim = 0
+
+    @property
+    def head_dim(self) -> int:
+        return self.rank + self.rope_dim
+
+
+@dataclass(frozen=True)
 class StateSpec:
     """State of fixed size per sequence, zero when the sequence starts."""
     shape: tuple[int, ...]
@@ -97,6 +115,8 @@ class LayerSpec:
     names: dict[str, str] = field(default_factory=dict)
     # gates on the sublayers' results, by the name under which the block arrangement takes them
     gates: dict[str, PartSpec] = field(default_factory=dict)
+    # constants of the block arrangement itself (keyword arguments of its class)
+    block_params: dict[str, Any] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)

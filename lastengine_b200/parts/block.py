@@ -1,5 +1,7 @@
 """Arrangement of a layer's parts.
 
+parallel_residual (at the end of this file): x += mult * (Mixer(norm(x)) + FeedForward(norm(x))).
+
 pre_norm_residual (src/dense.rs:178-194):
     x += [post_norm](Mixer(norm(x)));  x += [post_norm](FeedForward(norm(x)))
 The norms after the mixer and after the feed-forward are the reference's own lfm3 layout and
@@ -190,3 +192,52 @@ class GatedPreNormResidualBlock:
         self.ffn.forward(h2, y, False, batch, env)
         self.ffn_gate.add_gated(x, y, h2, env, next_norm=after_ffn, h_out=h if after_ffn is not None else None)
         return NormedRows(h, after_ffn) if after_ffn is not None else None
+
+
+@BLOCKS.register("parallel_residual")
+class ParallelResidualBlock:
+    """h = norm(x);  x += mult * (Mixer(h) + FeedForward(h)): one norm, both sublayers read its result,
+    their results are summed in float and enter the stream together, times a constant.  A layer may have
+    no feed-forward.  The kernel that adds the sum into x also leaves the norm of the new x for the next
+    block when that is of this arrangement too (with a layer norm) and nothing is added to the stream in
+    between, so a model runs one norm kernel, for its first layer."""
+
+    def __init__(self, mixer, ffn, mixer_norm, ffn_norm=None, post_mixer_norm=None, post_ffn_norm=None,
+                 mult: float = 1.0):
+        if ffn_norm is not None or post_mixer_norm is not None or post_ffn_norm is not None:
+            raise ValueError("the parallel arrangement has one norm, in front of both sublayers")
+        self.mixer, self.ffn, self.mixer_norm = mixer, ffn, mixer_norm
+        self.mult = float(mult)
+
+    def parts(self) -> dict[str, object]:
+        p = {"mixer": self.mixer, "mixer_norm": self.mixer_norm}
+        if self.ffn is not None:
+            p["ffn"] = self.ffn
+        return p
+
+    def first_reader(self):
+        return self.mixer_norm, self
+
+    def forward(self, x: torch.Tensor, batch, cache, env, pending=None):
+        from .norm import LayerNorm
+        M, D = x.shape
+        ws = env.workspace
+        env.split_in = env.split_out = None
+        if isinstance(pending, NormedRows) and pending.norm is self.mixer_norm and pending.values.shape == (M, D):
+            h = pending.values
+        else:
+            h = ws.get("block.h", (M, D), env.dtype)
+            self.mixer_norm.forward(h, x)
+        y = ws.get("block.t", (M, D), torch.float32)
+        self.mixer.forward(h, y, False, batch, cache, env)
+        if self.ffn is not None:
+            self.ffn.forward(h, y, True, batch, env)
+        nxt = env.next_block_norm
+        after = nxt[0] if nxt is not None and isinstance(nxt[1], ParallelResidualBlock) and isinstance(nxt[0], LayerNorm) \
+            else None
+        if after is None:
+            kernels.scaled_residual(x, y, self.mult)
+            return None
+        h2 = ws.get("block.h2" if h is ws.get("block.h", (M, D), env.dtype) else "block.h", (M, D), env.dtype)
+        kernels.scaled_residual(x, y, self.mult, h=h2, norm_w=after.weight, eps=after.eps)
+        return NormedRows(h2, after)

@@ -1,6 +1,6 @@
 """Token embedding and output head.
 
-x = embed[token] (src/dense.rs:172-177); logits = W_out . norm(x) with W_out the head's own
+x = embed[token] (src/dense.rs:172-177), times a constant where the design has one; logits = W_out . norm(x) with W_out the head's own
 matrix, or the embedding when the model ties them (src/dense.rs:195-196).  Logits are float.
 """
 from __future__ import annotations
@@ -14,8 +14,11 @@ from .base import EMBEDDING, MATRIX, BuildEnv, Part, TensorSpec
 
 @EMBEDDINGS.register("token_embedding")
 class TokenEmbedding(Part):
-    def __init__(self, vocab_size: int, hidden_size: int):
+    def __init__(self, vocab_size: int, hidden_size: int, scale: float = 1.0):
+        """`scale` multiplies the row on its way into the residual stream; the table itself (which a
+        tied output head multiplies with) stays as stored."""
         self.V, self.D = int(vocab_size), int(hidden_size)
+        self.scale = float(scale)
         self.weight: torch.Tensor | None = None
 
     def tensors(self) -> dict[str, TensorSpec]:
@@ -25,7 +28,7 @@ class TokenEmbedding(Part):
         self.weight = tensors["weight"].contiguous()
 
     def forward(self, x: torch.Tensor, tokens: torch.Tensor) -> None:
-        kernels.embed(x, self.weight, tokens)
+        kernels.embed(x, self.weight, tokens, self.scale)
 
 
 @HEADS.register("linear_head")

@@ -31,7 +31,7 @@ def fuse_gate_up(w1: torch.Tensor, w3: torch.Tensor, interleave: bool) -> torch.
     return torch.stack([g, u], dim=1).reshape(2 * F_, D).contiguous()
 
 
-_ACTIVATIONS = {"silu": kernels.SILU, "gelu_tanh": kernels.GELU_TANH}
+_ACTIVATIONS = {"silu": kernels.SILU, "gelu_tanh": kernels.GELU_TANH, "clamped_sigmoid": kernels.CLAMPED_SIGMOID}
 
 
 @FEED_FORWARDS.register("swiglu", "gated_dense")
@@ -44,8 +44,8 @@ class SwiGLU(FeedForward):
     def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu",
                  names: tuple[str, str, str] = ("w1.weight", "w3.weight", "w2.weight")):
         self.D, self.F = int(hidden_size), int(intermediate_size)
-        if activation not in _ACTIVATIONS:
-            raise ValueError(f"unknown feed-forward activation '{activation}' ({', '.join(sorted(_ACTIVATIONS))})")
+        if activation not in ("silu", "gelu_tanh"):
+            raise ValueError(f"unknown feed-forward activation '{activation}' (gelu_tanh, silu)")
         self.activation = activation
         self.act = _ACTIVATIONS[activation]
         self.n_gate, self.n_up, self.n_down = (str(n) for n in names)
@@ -84,38 +84,63 @@ class SwiGLU(FeedForward):
                        emit=emit if accumulate else None)
 
 
-@FEED_FORWARDS.register("sigmoid_topk_moe")
+@FEED_FORWARDS.register("sigmoid_topk_moe", "topk_moe")
 class SigmoidTopKMoE(FeedForward):
+    """Top-k experts of the gated shape.  Defaults: the sigmoid router described at the top of this file and
+    SwiGLU experts under the names `gate.weight`, `expert_bias`, `experts.<e>.w1/w3/w2.weight`.
+
+    `router="softmax_chosen"`: logits z = Wr h + bias (the bias is part of the logit), the k largest are
+    chosen (ties to the lower index) and weighted by the softmax over the chosen logits alone.
+    `activation="clamped_sigmoid"` with `limit` and `alpha`: g = min(W_gate h, limit),
+    u = clamp(W_up h, -limit, limit), y = g * sigmoid(alpha * g) * (u + 1).
+    `names`: "router", "bias", and "gate"/"up"/"down" with `{e}` standing for the expert's number."""
+
     def __init__(self, hidden_size: int, num_experts: int, top_k: int, expert_size: int,
                  norm_topk: bool = True, use_bias: bool = True, scaling: float = 1.0,
-                 bias_std: float = 0.1):
+                 bias_std: float = 0.1, router: str = "sigmoid", activation: str = "silu",
+                 limit: float = 0.0, alpha: float = 1.0, names: dict[str, str] | None = None):
         if not 1 <= top_k <= min(num_experts, 16):
             raise ValueError(f"top-{top_k} of {num_experts} experts: the router takes 1..min(experts, 16)")
         if num_experts > 256:
             raise ValueError(f"{num_experts} experts: the router takes at most 256")
+        if router not in ("sigmoid", "softmax_chosen"):
+            raise ValueError(f"unknown router '{router}' (sigmoid, softmax_chosen)")
+        if activation not in _ACTIVATIONS:
+            raise ValueError(f"unknown expert activation '{activation}' ({', '.join(sorted(_ACTIVATIONS))})")
+        if activation == "clamped_sigmoid" and not limit > 0:
+            raise ValueError(f"the clamped activation needs a positive limit, got {limit}")
         self.D, self.E, self.k, self.Fe = int(hidden_size), int(num_experts), int(top_k), int(expert_size)
         self.norm_topk, self.use_bias, self.scaling = bool(norm_topk), bool(use_bias), float(scaling)
         self.bias_std = float(bias_std)
+        self.router, self.act = router, _ACTIVATIONS[activation]
+        self.limit, self.alpha = float(limit), float(alpha)
+        self.n = {"router": "gate.weight", "bias": "expert_bias", "gate": "experts.{e}.w1.weight",
+                  "up": "experts.{e}.w3.weight", "down": "experts.{e}.w2.weight"}
+        self.n.update(names or {})
         self.router_w = self.router_b = self.w13 = self.w2 = None
         self.fused = False
 
     def tensors(self) -> dict[str, TensorSpec]:
-        t = {"gate.weight": TensorSpec((self.E, self.D), VECTOR)}
+        n = self.n
+        t = {n["router"]: TensorSpec((self.E, self.D), VECTOR)}
         if self.use_bias:
-            t["expert_bias"] = TensorSpec((self.E,), BIAS, std=self.bias_std)
+            t[n["bias"]] = TensorSpec((self.E,), BIAS, std=self.bias_std)
         for e in range(self.E):
-            t[f"experts.{e}.w1.weight"] = TensorSpec((self.Fe, self.D), MATRIX)
-            t[f"experts.{e}.w3.weight"] = TensorSpec((self.Fe, self.D), MATRIX)
-            t[f"experts.{e}.w2.weight"] = TensorSpec((self.D, self.Fe), MATRIX)
+            t[n["gate"].format(e=e)] = TensorSpec((self.Fe, self.D), MATRIX)
+            t[n["up"].format(e=e)] = TensorSpec((self.Fe, self.D), MATRIX)
+            t[n["down"].format(e=e)] = TensorSpec((self.D, self.Fe), MATRIX)
         return t
 
     def load(self, tensors, env: BuildEnv) -> None:
-        self.fused = (not env.is_float32) and self.Fe % 16 == 0
-        self.router_w = tensors["gate.weight"].contiguous()
-        self.router_b = tensors["expert_bias"].contiguous() if self.use_bias else None
-        self.w13 = torch.stack([fuse_gate_up(tensors[f"experts.{e}.w1.weight"], tensors[f"experts.{e}.w3.weight"],
+        n = self.n
+        # the products' gated epilogue knows silu and gelu; another activation runs as a kernel of its own
+        self.fused = (not env.is_float32) and self.Fe % 16 == 0 and self.act in (kernels.SILU, kernels.GELU_TANH)
+        self.epilogue = kernels.SWIGLU | (self.act << 8)
+        self.router_w = tensors[n["router"]].contiguous()
+        self.router_b = tensors[n["bias"]].contiguous() if self.use_bias else None
+        self.w13 = torch.stack([fuse_gate_up(tensors[n["gate"].format(e=e)], tensors[n["up"].format(e=e)],
                                              self.fused) for e in range(self.E)]).contiguous()
-        self.w2 = torch.stack([tensors[f"experts.{e}.w2.weight"] for e in range(self.E)]).contiguous()
+        self.w2 = torch.stack([tensors[n["down"].format(e=e)] for e in range(self.E)]).contiguous()
 
     def flops_per_row(self) -> int:
         return 2 * self.D * self.E + self.k * 6 * self.D * self.Fe       # the router, and k experts of three matrices
@@ -133,7 +158,8 @@ class SigmoidTopKMoE(FeedForward):
         ws = env.workspace
         ids = ws.get("moe.ids", (M, self.k), torch.int32)
         wts = ws.get("moe.w", (M, self.k), torch.float32)
-        kernels.moe_router(ids, wts, h, self.router_w, self.router_b, self.norm_topk, self.scaling)
+        kernels.moe_router(ids, wts, h, self.router_w, self.router_b, self.norm_topk, self.scaling,
+                           softmax_chosen=self.router == "softmax_chosen")
         offsets = ws.get("moe.offsets", (self.E + 1,), torch.int32)
         sorted_pair = ws.get("moe.sorted", (P,), torch.int32)
         pair_row = ws.get("moe.rows", (P,), torch.int32)
@@ -142,11 +168,14 @@ class SigmoidTopKMoE(FeedForward):
         kernels.gather_rows(xs, h, sorted_pair, div=self.k)
         a = ws.get("moe.a", (P, self.Fe), env.dtype)
         if self.fused:
-            kernels.linear(a, xs, self.w13, kernels.SWIGLU, group_offsets=offsets, rows_hint=P)
+            kernels.linear(a, xs, self.w13, self.epilogue, group_offsets=offsets, rows_hint=P)
         else:
             gu = ws.get("moe.gu", (P, 2 * self.Fe), torch.float32)
             kernels.linear(gu, xs, self.w13, group_offsets=offsets, rows_hint=P)
-            kernels.swiglu(a, gu)
+            if self.act == kernels.SILU:
+                kernels.swiglu(a, gu)
+            else:
+                kernels.gated_act(a, gu, self.act, self.limit, self.alpha)
         ys = ws.get("moe.ys", (P, self.D), torch.float32)
         kernels.linear(ys, a, self.w2, group_offsets=offsets, rows_hint=P)
         kernels.moe_combine(out, ys, pair_row, wts, accumulate)

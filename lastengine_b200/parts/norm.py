@@ -1,4 +1,5 @@
-"""RMSNorm: y = x / sqrt(mean(x^2) + eps) * w  (src/dense.rs:27-30).
+"""Norms.  RMSNorm: y = x / sqrt(mean(x^2) + eps) * w  (src/dense.rs:27-30); layer norm with a weight
+and no bias below it.
 
 `offset`: the weight is stored around zero and the factor is offset + w (1 + w in the designs that
 store it so); it is added once, in float, when the weights are loaded.  `tensor`: the weight's name
@@ -37,3 +38,28 @@ class RMSNorm(Part):
                 add: bool = False) -> None:
         """out = norm(x[rows]) (or out += norm(x) with add); x is the float residual or a float buffer."""
         kernels.rmsnorm(out, x, self.weight, self.eps, rows=rows, add=add)
+
+
+@NORMS.register("layernorm")
+class LayerNorm(Part):
+    """y = (x - mean(x)) / sqrt(var(x) + eps) * w with var the mean of the squared deviations; a weight,
+    no bias.  It takes a mean off the row, so it cannot be split between two products as the RMS norm is."""
+    splittable = False
+
+    def __init__(self, size: int, eps: float, tensor: str = "weight"):
+        self.size = int(size)
+        self.eps = float(eps)
+        self.tensor = str(tensor)
+        self.weight: torch.Tensor | None = None
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        return {self.tensor: TensorSpec((self.size,), NORM)}
+
+    def load(self, tensors: dict[str, torch.Tensor], env: BuildEnv) -> None:
+        self.weight = tensors[self.tensor].to(torch.float32).contiguous()
+
+    def forward(self, out: torch.Tensor, x: torch.Tensor, rows: torch.Tensor | None = None,
+                add: bool = False) -> None:
+        if add:
+            raise NotImplementedError("a layer norm added into the residual stream")
+        kernels.layernorm(out, x, self.weight, self.eps, rows=rows)
