@@ -130,6 +130,9 @@ def cmd_inspect(a) -> int:
     order = [e.layer for e in plan.schedule]
     if order != list(range(len(plan.layers))):
         print(f"  layers run in the order {' '.join(map(str, order))}")
+    for i, e in enumerate(plan.schedule):
+        if e.cache is not None and e.cache != i:
+            print(f"  layer {e.layer} reads what layer {plan.schedule[e.cache].layer} cached")
     ck = open_checkpoint(a.path)
     by: dict[tuple[str, str], list[int]] = {}
     total = 0

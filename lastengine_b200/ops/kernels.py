@@ -107,7 +107,7 @@ def _declare(L) -> None:
         "leb_latent_q_split": [P, P, P, I, P, P, I, I, I, I, I, I, P],
         "leb_heads_to_rows": [P, P, I, I, I, I, P],
         "leb_latent_attention": [P, I, P, P, P, P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
-        "leb_gemm_bf16_any": [P, I, P, P, I, I, I, I, I, I, P],
+        "leb_gemm_bf16_any": [P, I, P, P, I, I, I, I, I, I, P, I, S, P],
         "leb_gated_residual": [P, P, P, I, I, P, P, I, P, F, I, I, P],
         "leb_stream_add": [P, P, P, I, I, P],
         "leb_causal_conv": [P, I, P, I, I, P, P, P, P, P, P, I, I, I, I, I, P],
@@ -911,12 +911,15 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int = 
         return
     if x.dtype != torch.bfloat16:
         raise KernelError(f"linear: unsupported operand dtype {x.dtype}")
-    if group_offsets is None and (K % 8 != 0 or lda % 8 != 0 or x.data_ptr() % 16 != 0 or w.data_ptr() % 16 != 0
-                                  or not w.is_contiguous()):
+    if (K % 8 != 0 or lda % 8 != 0 or x.data_ptr() % 16 != 0 or w.data_ptr() % 16 != 0
+            or (group_offsets is None and not w.is_contiguous())):
         # sizes the tensor-core kernels do not take (they fetch 16 bytes at a time): the plain product
         if gated or scale is not None or emit is not None:
             raise KernelError(f"linear: an inner size of {K} (row stride {lda}) takes neither a gated epilogue nor a split norm")
-        _check(L.leb_gemm_bf16_any(_ptr(out), _dt(out, "linear.out"), _ptr(x), _ptr(w), M, N, K, lda, ldc, epilogue, _stream()))
+        if not w.is_contiguous():
+            raise KernelError("linear: the weights of a grouped product must be contiguous")
+        _check(L.leb_gemm_bf16_any(_ptr(out), _dt(out, "linear.out"), _ptr(x), _ptr(w), M, N, K, lda, ldc, epilogue,
+                                   _ptr(group_offsets), E, stride, _stream()))
         return
     hint = rows_hint if rows_hint > 0 else M
     tc = _OPTIONAL_TC[0]
