@@ -394,6 +394,16 @@ static int launch_latent(void* out, int ld_out, float* part, const void* qt, con
   return 0;
 }
 
+// The tensor-core kernel for bfloat16 (latent_attention_mma.cu) and its switch (on by default; off for comparisons).
+extern "C" int leb_latent_attention_mma_supported(int rank, int rot, int page_size);
+extern "C" int leb_latent_attention_mma(void* out, float* part, const void* qt, const void* qr, const void* pool,
+                                        const int* block_table, int bt_width, const int* seq_slot, const int* seq_pos0,
+                                        const int* seq_qstart, const int* seq_qlen, const float* sink, int M, int B, int H,
+                                        int rank, int rot, int page_size, float scale, int max_qlen, int n_splits,
+                                        cudaStream_t st);
+static int g_latent_mma = 1;
+LEB_API void leb_set_latent_mma(int on) { g_latent_mma = on ? 1 : 0; }
+
 // qt [H, M, rank] (queries taken into the latent space), qr [M, H, rot] (rotated parts), pool
 // [page][page_size][rank + rot], sink [H] float or null; out [H, M, ld_out] (ld_out >= rank, the
 // rest zeros).  part: float scratch of M*H*n_splits*(rank+2), used when n_splits > 1 (then every
@@ -412,12 +422,17 @@ LEB_API int leb_latent_attention(void* out, int ld_out, float* part, const void*
               "leb_latent_attention: splits need single-row sequences and scratch");
   LebPlainLaunches plain(true);
   int rc;
+  const bool mma = g_latent_mma && dtype == LEB_BF16 && ld_out == rank && leb_latent_attention_mma_supported(rank, rot, page_size) &&
+                   (((uintptr_t)qt | (uintptr_t)qr | (uintptr_t)pool) & 15) == 0;
 #define LEB_LAT(T, L)                                                                                              \
   launch_latent<T, L>(out, ld_out, part, qt, qr, pool, block_table, bt_width, seq_slot, seq_pos0, seq_qstart, seq_qlen, \
                       sink, M, B, H, rank, rot, page_size, scale, max_qlen, n_splits, st)
 #define LEB_LAT_T(T) \
   (rank <= 32 ? LEB_LAT(T, 1) : rank <= 64 ? LEB_LAT(T, 2) : rank <= 128 ? LEB_LAT(T, 4) : rank <= 256 ? LEB_LAT(T, 8) : LEB_LAT(T, 16))
-  if (dtype == LEB_F32) rc = LEB_LAT_T(float);
+  if (mma)
+    rc = leb_latent_attention_mma(out, part, qt, qr, pool, block_table, bt_width, seq_slot, seq_pos0, seq_qstart, seq_qlen,
+                                  sink, M, B, H, rank, rot, page_size, scale, max_qlen, n_splits, st);
+  else if (dtype == LEB_F32) rc = LEB_LAT_T(float);
   else if (dtype == LEB_BF16) rc = LEB_LAT_T(bf16);
   else return leb_fail("leb_latent_attention: unknown dtype %d", dtype);
 #undef LEB_LAT_T

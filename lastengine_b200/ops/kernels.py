@@ -107,6 +107,7 @@ def _declare(L) -> None:
         "leb_latent_q_split": [P, P, P, I, P, P, I, I, I, I, I, I, P],
         "leb_heads_to_rows": [P, P, I, I, I, I, P],
         "leb_latent_attention": [P, I, P, P, P, P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
+        "leb_latent_attention_mma_supported": [I, I, I],
         "leb_gemm_bf16_any": [P, I, P, P, I, I, I, I, I, I, P, I, S, P],
         "leb_gated_residual": [P, P, P, I, I, P, P, I, P, F, I, I, P],
         "leb_stream_add": [P, P, P, I, I, P],
@@ -158,6 +159,8 @@ def _declare(L) -> None:
     L.leb_launch_count.argtypes = []
     L.leb_sm_count.restype = c_int
     L.leb_sm_count.argtypes = []
+    L.leb_set_latent_mma.restype = None
+    L.leb_set_latent_mma.argtypes = [I]
     L.leb_retention_chunked_scratch.restype = ctypes.c_longlong
     L.leb_retention_chunked_scratch.argtypes = [I, I, I, I, I]
     for name, args in _OPTIONAL.items():
@@ -583,13 +586,31 @@ def heads_to_rows(out: torch.Tensor, src: torch.Tensor) -> None:
     _check(lib().leb_heads_to_rows(_ptr(out), _ptr(src), _dt(out, "heads_to_rows.out"), M, H, w, _stream()))
 
 
-def latent_attention_splits(batch, H: int) -> int:
-    """Pieces the key range of a decode step is cut into so that the blocks fill the SMs (1 for prompts)."""
+def latent_attention_uses_mma(dtype: torch.dtype, rank: int, rot: int, page_size: int, ld_out: int) -> bool:
+    """Whether `latent_attention` runs its tensor-core kernel for these sizes (bfloat16, a latent that is a
+    multiple of 32 up to 512, a rotated part that is a multiple of 16) or the general one."""
+    return bool(_LATENT_MMA[0] and dtype == torch.bfloat16 and ld_out == rank
+                and lib().leb_latent_attention_mma_supported(int(rank), int(rot), int(page_size)))
+
+
+_LATENT_MMA = [True]
+
+
+def set_latent_mma(on: bool) -> None:
+    """Turns the tensor-core latent attention off (the general kernel then serves bfloat16 too) or on again."""
+    _LATENT_MMA[0] = bool(on)
+    lib().leb_set_latent_mma(1 if on else 0)
+
+
+def latent_attention_splits(batch, H: int, mma: bool = False) -> int:
+    """Pieces the key range of a decode step is cut into so that the blocks fill the SMs (1 for prompts).
+    The tensor-core kernel takes up to 64 heads in a block that is alone on its SM, the general one 8 in
+    blocks of which an SM holds several; a piece is at least four tiles of 32 cached rows."""
     if batch.max_qlen != 1:
         return 1
-    blocks = batch.n_seqs * -(-H // 8)
+    blocks = batch.n_seqs * -(-H // (64 if mma else 8))
     tiles = -(-batch.max_kvlen // 32)
-    want = max(1, (2 * sm_count()) // max(1, blocks))
+    want = max(1, ((1 if mma else 2) * sm_count()) // max(1, blocks))
     return int(max(1, min(want, tiles // 4, 64)))
 
 

@@ -160,6 +160,9 @@ LAT_CASES = [   # heads, dim, rot_dim, vdim, q_rank, kv_rank, scale, rotated dim
     (4, 64, 64, 64, 96, 160, 0.08, 64, True),
     (2, 32, 8, 16, 48, 288, 0.05, 8, True),         # a latent beyond 256
     (2, 16, 0, 16, 24, 32, 0.2, 0, True),           # no rotated part at all
+    (16, 32, 16, 32, 64, 128, 0.1, 16, True),       # four rows of sixteen heads in a tensor-core block
+    (6, 16, 32, 24, 48, 96, 0.12, 32, True),        # ten rows of six heads; an odd number of tiles across the latent
+    (70, 8, 16, 8, 32, 32, 0.2, 16, True),          # more heads than a tensor-core block takes
 ]
 
 
@@ -237,6 +240,30 @@ def test_latent_attention_reaches_a_row_far_back_and_at_page_borders():
         head = rig.step([s], [h[:T - 3]])[0]
         tail = torch.cat([rig.step([s], [h[i:i + 1]])[0] for i in range(T - 3, T)])
         assert H.rel_err(torch.cat([head, tail]), want) < H.TOL_F32, f"far row at {far}"
+
+
+def test_tensor_core_and_general_latent_attention_agree():
+    """bfloat16: the same steps through the tensor-core kernel and through the general one."""
+    D = 64
+    m = lat(5, 16, 16, 24, 32, 64, 0.2, 5000.0)
+    hs = [inputs(n, D, 30 + n, True) for n in (200, 70, 1)]
+    outs = {}
+    assert K().latent_attention_uses_mma(torch.bfloat16, 64, 16, 64, 64)
+    assert not K().latent_attention_uses_mma(torch.float32, 64, 16, 64, 64)
+    assert not K().latent_attention_uses_mma(torch.bfloat16, 72, 16, 64, 72)
+    try:
+        for on in (True, False):
+            K().set_latent_mma(on)
+            rig = MixerRig(lat_params(D, m), "bfloat16", seed=4)
+            slots = [rig.cache.alloc_seq() for _ in hs]
+            got = rig.step(slots, [h[:-2] if h.shape[0] > 2 else h for h in hs])
+            tails = [rig.step(slots[:2], [h[i:i + 1] for h in hs[:2]]) for i in (-2, -1)]
+            outs[on] = torch.cat(got + [t for pair in tails for t in pair])
+    finally:
+        K().set_latent_mma(True)
+    want = torch.cat([P.latent_attention_mixer(h, rig.plain, m, 1e-5, P.round_bf16) for h in hs])
+    assert H.rel_err(outs[True], outs[False]) < H.TOL_BF16 / 3
+    assert H.rel_err(outs[True][:198], want[:198]) < H.TOL_BF16
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
