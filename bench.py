@@ -25,8 +25,8 @@ A step is one decode step of the whole batch.  One JSON line goes to stdout:
 
 Weights (1.8 GB) are far larger than L2, so consecutive steps cannot be served from L2.
 
-`--compare zekivik` leaves all of that aside and prints a line of its own: prompt and decode times of the
-Zekivik design at a few layer sizes beside the LFM3 hybrid at equal sizes, with every kernel entry point's time.
+`--compare zekivik` (or `lenesun`) leaves all of that aside and prints a line of its own: prompt and decode times
+of that design at a few layer sizes beside the closest LFM3 model at equal sizes, with every kernel entry point's time.
 """
 from __future__ import annotations
 
@@ -346,6 +346,62 @@ def _new_kernel_bytes(cfg: dict, rows: int, batch: int) -> dict:
     return out
 
 
+# ---- the Lenesun design beside an LFM3 model of attention layers with experts (--compare lenesun) --------
+def lenesun_config(width: int, heads: int, dim: int, rot_dim: int, vdim: int, q_rank: int, kv_rank: int,
+                   experts: int, top: int, ff: int, layers: int, vocab: int) -> dict:
+    """Latent attention and experts in every layer; the last two layers read the rows the layer before them cached."""
+    def mixer(kv_from=None):
+        m = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank,
+             "scale": (dim + rot_dim) ** -0.5, "rot": {"dims": rot_dim, "base": 10000.0}}
+        if kv_from is not None:
+            m["kv_from"] = kv_from
+        return m
+    mlp = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff, "limit": 7.0}}
+    ls = [{"type": "latent_attention", "mixer": mixer(layers - 3 if i >= layers - 2 else None), "mlp": mlp}
+          for i in range(layers)]
+    return {"architecture": "Lenesun", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+            "embedding": {"scale": 1.0}, "layers": ls}
+
+
+def lfm3_moe_like(width: int, heads: int, dim: int, experts: int, top: int, ff: int, layers: int, vocab: int) -> dict:
+    """The closest existing design at the same sizes: attention in every layer (as many heads of the same
+    unrotated size, grouped four to a key/value head) and as many experts of the same width per layer."""
+    return {"architectures": ["Lfm3ForCausalLM"], "model_type": "lfm3", "vocab_size": vocab, "hidden_size": width,
+            "num_hidden_layers": layers, "layer_types": ["attention"] * layers, "num_attention_heads": heads,
+            "num_key_value_heads": max(1, heads // 4), "head_dim": dim, "intermediate_size": ff,
+            "block_auto_adjust_ff_dim": False, "rope_theta": 10000.0, "conv_L_cache": 4, "norm_eps": 1e-5,
+            "num_experts": experts, "num_experts_per_tok": top, "moe_intermediate_size": ff, "num_dense_layers": 0,
+            "tie_embedding": True, "max_position_embeddings": 128000}
+
+
+LENESUN_SIZES = {
+    "w2048": dict(width=2048, heads=16, dim=128, rot_dim=64, vdim=128, q_rank=768, kv_rank=512, experts=32, top=4, ff=1024, layers=6),
+    "w1024": dict(width=1024, heads=8, dim=64, rot_dim=32, vdim=64, q_rank=384, kv_rank=256, experts=16, top=2, ff=512, layers=6),
+}
+
+
+def _lenesun_kernel_work(cfg: dict, rows: int, batch: int, context: int) -> dict:
+    """What a step's launches of the design's own kernels have to move (bytes) or compute (flops), by entry point."""
+    W = cfg["width"]
+    out = {"leb_layernorm": rows * W * 6, "leb_scaled_residual": 0, "leb_latent_prep": 0, "leb_latent_q_split": 0,
+           "leb_heads_to_rows": 0, "leb_gated_act": 0, "leb_latent_attention": 0}
+    attn_flops = 0
+    pairs = rows * (rows + 1) // 2 if batch == 1 and rows > 1 else rows * context
+    for l in cfg["layers"]:
+        m = l["mixer"]
+        H, dk = m["heads"], m["kv_rank"] + m["rot_dim"]
+        own = "kv_from" not in m
+        out["leb_scaled_residual"] += rows * W * 14                       # x read and written, the sum read, the norm written
+        out["leb_latent_prep"] += rows * (m["q_rank"] * 4 + (dk * 4 if own else 0))
+        out["leb_latent_q_split"] += rows * H * (m["dim"] + m["rot_dim"]) * 4
+        out["leb_heads_to_rows"] += rows * H * m["vdim"] * 4
+        if l["mlp"]:
+            out["leb_gated_act"] += rows * l["mlp"]["router"]["top"] * l["mlp"]["expert"]["ff"] * (8 + 2)
+        attn_flops += 2 * H * (dk + m["kv_rank"]) * pairs
+        out["leb_latent_attention"] += batch * context * dk * 2 + rows * H * (dk + m["kv_rank"]) * 2
+    return {"bytes": out, "attention_flops": attn_flops}
+
+
 def compare_designs(which: str, steps: int, warmup: int) -> int:
     import numpy as np
     import torch
@@ -354,12 +410,16 @@ def compare_designs(which: str, steps: int, warmup: int) -> int:
     pk, pk_src = peaks()
     rng = np.random.default_rng(0)
     results = {}
-    for size_name, sz in COMPARE_SIZES.items():
-        zc = zekivik_config(vocab=32768, **sz)
-        runs = sz["layers"] + 2
-        lc = lfm3_like(sz["width"], sz["ff"], sz["heads"], sz["kv_heads"], sz["dim"], runs, 32768)
+    for size_name, sz in (COMPARE_SIZES if which == "zekivik" else LENESUN_SIZES).items():
+        if which == "zekivik":
+            zc = zekivik_config(vocab=32768, **sz)
+            runs = sz["layers"] + 2
+            lc = lfm3_like(sz["width"], sz["ff"], sz["heads"], sz["kv_heads"], sz["dim"], runs, 32768)
+        else:
+            zc = lenesun_config(vocab=32768, **sz)
+            lc = lfm3_moe_like(sz["width"], sz["heads"], sz["dim"], sz["experts"], sz["top"], sz["ff"], sz["layers"], 32768)
         row = {}
-        for label, cfg in (("zekivik", zc), ("lfm3", lc)):
+        for label, cfg in ((which, zc), ("lfm3", lc)):
             eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=8 * 2304 + 4096, max_seqs=16)
             nums = model_numbers(eng)
             r = {"weights_gb": round(nums["weight_bytes"] / 1e9, 3)}
@@ -396,7 +456,18 @@ def compare_designs(which: str, steps: int, warmup: int) -> int:
                 eng.step(seqs, [[2]] * 8, "last")
             eng.release(seqs)
             dec_k = t.summary()
-            by = {"prefill": _new_kernel_bytes(zc, PREFILL_TOKENS, 1), "decode_b8": _new_kernel_bytes(zc, 8, 8)} if label == "zekivik" else {}
+            by, fl = {}, {}
+            if label == "zekivik":
+                by = {"prefill": _new_kernel_bytes(zc, PREFILL_TOKENS, 1), "decode_b8": _new_kernel_bytes(zc, 8, 8)}
+            elif label == "lenesun":
+                wp, wd = _lenesun_kernel_work(zc, PREFILL_TOKENS, 1, PREFILL_TOKENS), _lenesun_kernel_work(zc, 8, 8, 2048)
+                by = {"prefill": {k: v for k, v in wp["bytes"].items() if k != "leb_latent_attention"}, "decode_b8": wd["bytes"]}
+                fl = {"prefill": {"leb_latent_attention": wp["attention_flops"]}}
+            else:     # the other design's attention, for the comparison: flops of a prompt, cache bytes of a decode step
+                att = nums["attn_flops_per_qk"] * PREFILL_TOKENS * (PREFILL_TOKENS + 1) // 2
+                fl = {"prefill": {"leb_attention_prefill_tc": att, "leb_attention_prefill": att}}
+                by = {"decode_b8": {"leb_attention_decode": 8 * 2048 * nums["kv_bytes_per_token"],
+                                    "leb_attention_decode_prep": 8 * 2048 * nums["kv_bytes_per_token"]}}
             for where, summ in (("prefill", pre_k), ("decode_b8", dec_k)):
                 ks = {}
                 for name, (calls, ms) in summ.items():
@@ -405,13 +476,18 @@ def compare_designs(which: str, steps: int, warmup: int) -> int:
                     if nb and ms > 0:
                         e["gb_s"] = round(nb / (ms / 1e3) / 1e9, 1)
                         e["frac_of_hbm"] = round(nb / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 3)
+                    nf = fl.get(where, {}).get(name)
+                    if nf and ms > 0:
+                        e["tflops"] = round(nf / (ms / 1e3) / 1e12, 1)
+                        e["frac_of_bf16_peak"] = round(nf / (ms / 1e3) / 1e12 / pk["bf16_tflops"], 3)
                     ks[name] = e
                 r[f"kernels_{where}"] = ks
             row[label] = r
             del eng
             torch.cuda.empty_cache()
         results[size_name] = {"sizes": sz, **row}
-    print(json.dumps({"compare": which, "against": "lfm3 hybrid at equal layer sizes", "dtype": "bf16",
+    print(json.dumps({"compare": which, "against": "lfm3 hybrid at equal layer sizes" if which == "zekivik" else
+                      "lfm3 with attention and experts in every layer at equal layer sizes", "dtype": "bf16",
                       "data": "synthetic (random weights, uniform random token ids)", "peaks": pk_src,
                       "prefill_tokens": PREFILL_TOKENS, "decode_context": 2048, "steps": steps, "warmup": warmup,
                       "sizes": results}))
@@ -436,7 +512,7 @@ def main() -> int:
     ap.add_argument("--unequal", type=int, default=0, metavar="N",
                     help="instead of the default run: N requests with prompts of U[64, 2048] tokens generate "
                          "--steps tokens each in one batch through the Python entry point (prints its own JSON line)")
-    ap.add_argument("--compare", default="", choices=["", "zekivik"],
+    ap.add_argument("--compare", default="", choices=["", "zekivik", "lenesun"],
                     help="instead of the default run: prefill and decode of that design at a few layer sizes beside "
                          "the LFM3 hybrid at equal sizes, with every kernel's time (prints its own JSON line)")
     args = ap.parse_args()

@@ -63,12 +63,22 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
   return g / (1.0f + expf(-g)) * u;
 }
 // A gated epilogue (code 2: act(gate) * up over interleaved weight rows) names its activation in the
-// upper bits of the epilogue code the kernels get: 0 silu, 1 the tanh form of gelu.  The entry
-// points take the same combined code, check it, and hand it on through LEB_EPI_ARG at the launch.
+// upper bits of the epilogue code the kernels get: 0 silu, 1 the tanh form of gelu, 2 the clamped
+// sigmoid form g' sigmoid(1.702 g') (u' + 1) with g' = min(g, L), u' = clamp(u, -L, L), whose limit L
+// rides above the code as the upper 16 bits of its float (a limit that bfloat16 holds exactly).  The
+// entry points take the same combined code, check it, and hand it on through LEB_EPI_ARG at the launch.
 extern thread_local int g_leb_gate_act;
 #define LEB_EPI_ARG(e) ((e) | (g_leb_gate_act << 8))
+#define LEB_GATE_ACT_OK(act, epi) ((act) == 0 || (((act) == 1 || ((act) & 255) == 2) && (epi) == 2))
 template <typename T>
 __device__ __forceinline__ float gate_mul(float g, float u, int act) {
+  if ((act & 255) == 2) {
+    const float lim = __uint_as_float(((unsigned)act >> 8) << 16);
+    g = fminf(g, lim);
+    u = fminf(fmaxf(u, -lim), lim);
+    if (sizeof(T) == 2) return __fdividef(g, 1.0f + __expf(-1.702f * g)) * (u + 1.0f);
+    return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+  }
   if (act == 1) {
     const float z = 0.7978845608028654f * (g + 0.044715f * g * g * g);
     float t;

@@ -210,7 +210,7 @@ LEB_API int leb_gemm_bf16_small(void* C, int c_dtype, const void* A, const void*
                                 cudaStream_t st) {
   const int act_ = epilogue >> 8;
   epilogue &= 255;
-  LEB_REQUIRE(act_ == 0 || (act_ == 1 && epilogue == 2), "leb_gemm_bf16_small: activation %d goes with the gated epilogue only", act_);
+  LEB_REQUIRE(LEB_GATE_ACT_OK(act_, epilogue), "leb_gemm_bf16_small: activation %d goes with the gated epilogue only", act_);
   g_leb_gate_act = act_;
   if (M <= 0 || N <= 0) return 0;
   LEB_REQUIRE(K > 0 && K % 8 == 0, "leb_gemm_bf16_small: K (%d) must be a multiple of 8", K);

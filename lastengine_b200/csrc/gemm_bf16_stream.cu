@@ -529,7 +529,7 @@ LEB_API int leb_gemm_bf16_stream(void* C, int c_dtype, const void* A, const void
                                  void* emit_vals, const float* emit_g, float* emit_ssq, cudaStream_t st) {
   const int act_ = epilogue >> 8;
   epilogue &= 255;
-  LEB_REQUIRE(act_ == 0 || (act_ == 1 && epilogue == 2), "leb_gemm_bf16_stream: activation %d goes with the gated epilogue only", act_);
+  LEB_REQUIRE(LEB_GATE_ACT_OK(act_, epilogue), "leb_gemm_bf16_stream: activation %d goes with the gated epilogue only", act_);
   g_leb_gate_act = act_;
   if (M <= 0 || N <= 0) return 0;
   LEB_REQUIRE(M <= 16, "leb_gemm_bf16_stream: %d rows; this kernel takes at most 16", M);
@@ -587,7 +587,7 @@ LEB_API int leb_gemm_bf16_stream_grouped(void* C, int c_dtype, const void* A, co
                                          size_t w_group_stride, cudaStream_t st) {
   const int act_ = epilogue >> 8;
   epilogue &= 255;
-  LEB_REQUIRE(act_ == 0 || (act_ == 1 && epilogue == 2), "leb_gemm_bf16_stream_grouped: activation %d goes with the gated epilogue only", act_);
+  LEB_REQUIRE(LEB_GATE_ACT_OK(act_, epilogue), "leb_gemm_bf16_stream_grouped: activation %d goes with the gated epilogue only", act_);
   g_leb_gate_act = act_;
   if (P <= 0 || N <= 0 || n_groups <= 0) return 0;
   LEB_REQUIRE(n_groups <= ST_MAX_GROUPS, "leb_gemm_bf16_stream_grouped: %d groups; at most %d", n_groups, ST_MAX_GROUPS);

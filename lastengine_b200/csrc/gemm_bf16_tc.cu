@@ -347,7 +347,7 @@ LEB_API int leb_gemm_bf16_tc(void* C, int c_dtype, const void* A, const void* W,
                              int ldc, int epilogue, int* status, cudaStream_t st) {
   const int act_ = epilogue >> 8;
   epilogue &= 255;
-  LEB_REQUIRE(act_ == 0 || (act_ == 1 && epilogue == 2), "leb_gemm_bf16_tc: activation %d goes with the gated epilogue only", act_);
+  LEB_REQUIRE(LEB_GATE_ACT_OK(act_, epilogue), "leb_gemm_bf16_tc: activation %d goes with the gated epilogue only", act_);
   g_leb_gate_act = act_;
   if (M <= 0 || N <= 0) return 0;
   LEB_REQUIRE(leb_gemm_bf16_tc_supported(A, W, K, lda), "leb_gemm_bf16_tc: operands not aligned for TMA (K %d, lda %d)", K, lda);
@@ -405,7 +405,7 @@ LEB_API int leb_gemm_bf16_tc_sliced(void* C, int c_dtype, const void* A, const v
                                     int ldc, int epilogue, float* part, int n_slices, int* status, cudaStream_t st) {
   const int act_ = epilogue >> 8;
   epilogue &= 255;
-  LEB_REQUIRE(act_ == 0 || (act_ == 1 && epilogue == 2), "leb_gemm_bf16_tc_sliced: activation %d goes with the gated epilogue only", act_);
+  LEB_REQUIRE(LEB_GATE_ACT_OK(act_, epilogue), "leb_gemm_bf16_tc_sliced: activation %d goes with the gated epilogue only", act_);
   g_leb_gate_act = act_;
   if (M <= 0 || N <= 0) return 0;
   LEB_REQUIRE(leb_gemm_bf16_tc_supported(A, W, K, lda), "leb_gemm_bf16_tc_sliced: operands not aligned for TMA (K %d, lda %d)", K, lda);
@@ -432,7 +432,7 @@ LEB_API int leb_gemm_bf16_tc_grouped(void* C, int c_dtype, const void* A, const 
                                      cudaStream_t st) {
   const int act_ = epilogue >> 8;
   epilogue &= 255;
-  LEB_REQUIRE(act_ == 0 || (act_ == 1 && epilogue == 2), "leb_gemm_bf16_tc_grouped: activation %d goes with the gated epilogue only", act_);
+  LEB_REQUIRE(LEB_GATE_ACT_OK(act_, epilogue), "leb_gemm_bf16_tc_grouped: activation %d goes with the gated epilogue only", act_);
   g_leb_gate_act = act_;
   if (P <= 0 || N <= 0 || n_groups <= 0) return 0;
   LEB_REQUIRE(n_groups <= TC_MAX_GROUPS, "leb_gemm_bf16_tc_grouped: %d groups; at most %d", n_groups, TC_MAX_GROUPS);

@@ -325,7 +325,7 @@ LEB_API int leb_gemm_bf16_tc2(void* C, int c_dtype, const void* A, const void* W
                               int ldc, int epilogue, int* status, cudaStream_t st) {
   const int act_ = epilogue >> 8;
   epilogue &= 255;
-  LEB_REQUIRE(act_ == 0 || (act_ == 1 && epilogue == 2), "leb_gemm_bf16_tc2: activation %d goes with the gated epilogue only", act_);
+  LEB_REQUIRE(LEB_GATE_ACT_OK(act_, epilogue), "leb_gemm_bf16_tc2: activation %d goes with the gated epilogue only", act_);
   g_leb_gate_act = act_;
   if (M <= 0 || N <= 0) return 0;
   LEB_REQUIRE(K > 0 && K % 8 == 0 && lda % 8 == 0 && ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0,

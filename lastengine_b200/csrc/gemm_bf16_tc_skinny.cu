@@ -428,7 +428,7 @@ LEB_API int leb_gemm_bf16_skinny(void* C, int c_dtype, const void* A, const void
                                  cudaStream_t st) {
   const int act_ = epilogue >> 8;
   epilogue &= 255;
-  LEB_REQUIRE(act_ == 0 || (act_ == 1 && epilogue == 2), "leb_gemm_bf16_skinny: activation %d goes with the gated epilogue only", act_);
+  LEB_REQUIRE(LEB_GATE_ACT_OK(act_, epilogue), "leb_gemm_bf16_skinny: activation %d goes with the gated epilogue only", act_);
   g_leb_gate_act = act_;
   if (M <= 0 || N <= 0) return 0;
   LEB_REQUIRE(leb_gemm_bf16_skinny_supported(A, W, M, K, lda), "leb_gemm_bf16_skinny: takes 1..128 rows and TMA-aligned operands (M %d, K %d, lda %d)", M, K, lda);

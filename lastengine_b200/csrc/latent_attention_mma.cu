@@ -4,11 +4,11 @@
 //
 // A block of 8 warps owns one sequence, up to 64 query vectors (QT rows x HC heads; all heads read the
 // same cached rows, so heads stack into the M dimension of the products) and one split of the key
-// range.  Cached rows [c | k^r] come in tiles of 32 through two shared-memory stages filled by
-// asynchronous copies, the next tile travelling under the current one's products.  Per tile:
-//   S = Q K^T        64 x 32 over rank + rot     warp (m-tile of 16 vectors, 16 of the keys), mma.sync m16n8k16
+// range.  Cached rows [c | k^r] come in tiles of BN = 64 (32 for latents beyond 256) through two shared-memory
+// stages filled by asynchronous copies, the next tile travelling under the current one's products.  Per tile:
+//   S = Q K^T        64 x BN over rank + rot     warp (m-tile of 16 vectors, half of the keys), mma.sync m16n8k16
 //   softmax          float: a warp per 8 vectors, a lane per key; running maximum and sum in registers
-//   O = O corr + P V 64 x rank over the 32 keys  warp (32 vectors, a quarter of the latent), P as bfloat16,
+//   O = O corr + P V 64 x rank over the BN keys  warp (32 vectors, a quarter of the latent), P as bfloat16,
 //                    V = the first `rank` numbers of the same staged rows, read transposed by ldmatrix
 // The accumulators of O (64 x rank floats, 128 registers a thread at rank 512) are why the latent is
 // cut over four warps and a block is alone on its SM.  At the end the sink joins the denominator (or,
@@ -16,7 +16,6 @@
 #include "common.cuh"
 
 #define LM_BM 64
-#define LM_BN 32
 #define LM_NEG (-1e30f)
 
 __device__ __forceinline__ void lm_mma(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
@@ -39,7 +38,9 @@ __device__ __forceinline__ void lm_commit() { asm volatile("cp.async.commit_grou
 __device__ __forceinline__ void lm_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
 __device__ __forceinline__ uint32_t lm_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-template <int NT>      // n8-tiles of the latent a warp sums at most: rank <= 32 * NT
+// NT: n8-tiles of the latent a warp sums at most (rank <= 32 * NT).  BN: cached rows per tile, 64 where two
+// stages of them fit shared memory beside the queries (rows of up to 512 numbers), else 32.
+template <int NT, int BN>
 __global__ void __launch_bounds__(256, 1)
 latent_attention_mma_kernel(bf16* __restrict__ out, float* __restrict__ part, const bf16* __restrict__ qt,
                             const bf16* __restrict__ qr, const bf16* __restrict__ pool,
@@ -63,13 +64,16 @@ latent_attention_mma_kernel(bf16* __restrict__ out, float* __restrict__ part, co
   const int R = nrows * HC;                  // vectors r = i * HC + j in use (those with j >= nheads are idle)
   const int dk = rank + rot;
   const int LDK = dk + 8;                    // row stride in elements: an odd number of 16-byte pieces
-  const int LDP = LM_BN + 8;
+  constexpr int LM_BN = BN;
+  constexpr int LDP = BN + 8;
+  constexpr int LDS = BN + 1;
+  constexpr int KW = BN / 2;                 // keys of a warp's part of S
   const int ntu = rank / 32;                 // n8-tiles of the latent per warp
 
   bf16* q_s = reinterpret_cast<bf16*>(lm_sm);                      // [64][LDK]
   bf16* k_s = q_s + LM_BM * LDK;                                   // [2][32][LDK]
-  float* s_s = reinterpret_cast<float*>(k_s + 2 * LM_BN * LDK);    // [64][33]
-  bf16* p_s = reinterpret_cast<bf16*>(s_s + LM_BM * 33);           // [64][LDP]
+  float* s_s = reinterpret_cast<float*>(k_s + 2 * LM_BN * LDK);    // [64][BN + 1]
+  bf16* p_s = reinterpret_cast<bf16*>(s_s + LM_BM * LDS);          // [64][LDP]
   float* c_s = reinterpret_cast<float*>(p_s + LM_BM * LDP);        // [64]
 
   if (slot < 0) {                            // a padding sequence: defined output, no cache access
@@ -139,12 +143,12 @@ latent_attention_mma_kernel(bf16* __restrict__ out, float* __restrict__ part, co
   for (int rr = 0; rr < 8; rr++) { mx[rr] = LM_NEG; l[rr] = 0.f; }
 
   const int g = lane >> 2, tg = lane & 3;
-  // S: this warp's 16 vectors and 16 keys;  O: this warp's 32 vectors and quarter of the latent
+  // S: this warp's 16 vectors and half of the tile's keys;  O: this warp's 32 vectors and quarter of the latent
   const int s_mt = warp >> 1, s_kh = warp & 1;
   const int o_mh = warp >> 2, o_dq = warp & 3;
   const int dim0 = o_dq * 8 * ntu;
   const uint32_t q_addr = lm_smem(q_s + (size_t)(16 * s_mt + (lane & 7) + ((lane >> 3) & 1) * 8) * LDK + (lane >> 4) * 8);
-  const uint32_t kb_off = (uint32_t)(((16 * s_kh + (lane & 7) + (lane >> 4) * 8) * LDK + ((lane >> 3) & 1) * 8) * 2);
+  const uint32_t kb_off = (uint32_t)(((KW * s_kh + (lane & 7) + (lane >> 4) * 8) * LDK + ((lane >> 3) & 1) * 8) * 2);
   const uint32_t vb_off = (uint32_t)((((lane & 7) + ((lane >> 3) & 1) * 8) * LDK + dim0 + (lane >> 4) * 8) * 2);
   const uint32_t p_addr = lm_smem(p_s + (size_t)(32 * o_mh + (lane & 7) + ((lane >> 3) & 1) * 8) * LDP + (lane >> 4) * 8);
 
@@ -157,44 +161,68 @@ latent_attention_mma_kernel(bf16* __restrict__ out, float* __restrict__ part, co
     const int key0 = tile * LM_BN;
     const uint32_t k_base = lm_smem(k_s + (size_t)stage * LM_BN * LDK);
 
-    // ---- S = Q K^T ----
+    // ---- S = Q K^T ----  (even and odd slices of the inner size in accumulators of their own: with two
+    // warps per scheduler the products of one accumulator chain would wait for one another)
     if (16 * s_mt < R) {
-      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-      for (int ks = 0; ks < dk; ks += 16) {
-        uint32_t a[4], bb[4];
-        lm_ldsm4(a, q_addr + ks * 2);
-        lm_ldsm4(bb, k_base + kb_off + ks * 2);
-        lm_mma(s[0], a, bb[0], bb[1]);
-        lm_mma(s[1], a, bb[2], bb[3]);
+      float s[2][KW / 8][4];
+#pragma unroll
+      for (int c = 0; c < 2; c++)
+#pragma unroll
+        for (int nt = 0; nt < KW / 8; nt++)
+#pragma unroll
+          for (int e = 0; e < 4; e++) s[c][nt][e] = 0.f;
+      for (int ks = 0; ks < dk; ks += 32) {
+#pragma unroll
+        for (int c = 0; c < 2; c++) {
+          if (ks + 16 * c >= dk) break;
+          uint32_t a[4];
+          lm_ldsm4(a, q_addr + (ks + 16 * c) * 2);
+#pragma unroll
+          for (int np = 0; np < KW / 16; np++) {
+            uint32_t bb[4];
+            lm_ldsm4(bb, k_base + kb_off + (uint32_t)(np * 16 * LDK * 2) + (ks + 16 * c) * 2);
+            lm_mma(s[c][2 * np], a, bb[0], bb[1]);
+            lm_mma(s[c][2 * np + 1], a, bb[2], bb[3]);
+          }
+        }
       }
 #pragma unroll
       for (int half = 0; half < 2; half++) {
         const int r = 16 * s_mt + g + 8 * half;
         const int qpos = pos0 + row_lo + r / HC;
 #pragma unroll
-        for (int nt = 0; nt < 2; nt++)
+        for (int nt = 0; nt < KW / 8; nt++)
 #pragma unroll
           for (int e = 0; e < 2; e++) {
-            const int col = 16 * s_kh + 8 * nt + 2 * tg + e;
-            s_s[r * 33 + col] = key0 + col <= qpos ? s[nt][2 * half + e] * scale : LM_NEG;
+            const int col = KW * s_kh + 8 * nt + 2 * tg + e;
+            s_s[r * LDS + col] = key0 + col <= qpos ? (s[0][nt][2 * half + e] + s[1][nt][2 * half + e]) * scale : LM_NEG;
           }
       }
     }
     __syncthreads();
 
-    // ---- softmax over the tile's keys, a lane per key ----
+    // ---- softmax over the tile's keys, a lane per key (two keys with tiles of 64) ----
 #pragma unroll
     for (int rr = 0; rr < 8; rr++) {
       const int r = 8 * warp + rr;
       if (r >= R) break;
-      const float sv = s_s[r * 33 + lane];
-      const bool valid = sv > 0.5f * LM_NEG;
-      const float mn = fmaxf(mx[rr], warp_max(sv));
-      const float p = valid ? expf(sv - mn) : 0.f;
+      float sv[BN / 32], p[BN / 32];
+      float tmax = LM_NEG, tsum = 0.f;
+#pragma unroll
+      for (int c = 0; c < BN / 32; c++) {
+        sv[c] = s_s[r * LDS + lane + 32 * c];
+        tmax = fmaxf(tmax, sv[c]);
+      }
+      const float mn = fmaxf(mx[rr], warp_max(tmax));
+#pragma unroll
+      for (int c = 0; c < BN / 32; c++) {
+        p[c] = sv[c] > 0.5f * LM_NEG ? expf(sv[c] - mn) : 0.f;
+        tsum += p[c];
+        p_s[r * LDP + lane + 32 * c] = __float2bfloat16_rn(p[c]);
+      }
       const float corr = expf(mx[rr] - mn);
-      l[rr] = l[rr] * corr + warp_sum(p);
+      l[rr] = l[rr] * corr + warp_sum(tsum);
       mx[rr] = mn;
-      p_s[r * LDP + lane] = __float2bfloat16_rn(p);
       if (lane == 0) c_s[r] = corr;
     }
     __syncthreads();
@@ -211,7 +239,7 @@ latent_attention_mma_kernel(bf16* __restrict__ out, float* __restrict__ part, co
       }
     }
 #pragma unroll
-    for (int ks = 0; ks < 2; ks++) {
+    for (int ks = 0; ks < BN / 16; ks++) {
       uint32_t a[2][4];
       lm_ldsm4(a[0], p_addr + ks * 32);
       lm_ldsm4(a[1], p_addr + 16 * LDP * 2 + ks * 32);
@@ -284,10 +312,10 @@ latent_attention_mma_kernel(bf16* __restrict__ out, float* __restrict__ part, co
 
 // Whether the tensor-core kernel takes these sizes (bfloat16 only; the caller checks the type).
 LEB_API int leb_latent_attention_mma_supported(int rank, int rot, int page_size) {
-  return rank >= 32 && rank <= 512 && rank % 32 == 0 && rot >= 0 && rot <= 256 && rot % 16 == 0 && page_size % LM_BN == 0;
+  return rank >= 32 && rank <= 512 && rank % 32 == 0 && rot >= 0 && rot <= 256 && rot % 16 == 0 && page_size % 64 == 0;
 }
 
-template <int NT>
+template <int NT, int BN>
 static int launch_latent_mma(bf16* out, float* part, const bf16* qt, const bf16* qr, const bf16* pool,
                              const int* block_table, int bt_width, const int* seq_slot, const int* seq_pos0,
                              const int* seq_qstart, const int* seq_qlen, const float* sink, int M, int B, int H, int rank,
@@ -296,8 +324,8 @@ static int launch_latent_mma(bf16* out, float* part, const bf16* qt, const bf16*
   int QT = LM_BM / HC;
   if (QT > max_qlen) QT = max_qlen;
   const int dk = rank + rot;
-  const size_t smem = (size_t)(LM_BM + 2 * LM_BN) * (dk + 8) * 2 + (size_t)LM_BM * 33 * 4 + (size_t)LM_BM * (LM_BN + 8) * 2 + LM_BM * 4;
-  auto kern = latent_attention_mma_kernel<NT>;
+  const size_t smem = (size_t)(LM_BM + 2 * BN) * (dk + 8) * 2 + (size_t)LM_BM * (BN + 1) * 4 + (size_t)LM_BM * (BN + 8) * 2 + LM_BM * 4;
+  auto kern = latent_attention_mma_kernel<NT, BN>;
   static size_t smem_set = 0;
   if (smem > 48 * 1024 && smem > smem_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -326,13 +354,13 @@ LEB_API int leb_latent_attention_mma(void* out, float* part, const void* qt, con
               "leb_latent_attention_mma: splits need single-row sequences and scratch");
   LEB_REQUIRE((((uintptr_t)qt | (uintptr_t)qr | (uintptr_t)pool) & 15) == 0, "leb_latent_attention_mma: operands must be 16-byte aligned");
   LebPlainLaunches plain(true);
-#define LEB_LM(NT_)                                                                                                       \
-  launch_latent_mma<NT_>((bf16*)out, part, (const bf16*)qt, (const bf16*)qr, (const bf16*)pool, block_table, bt_width, \
-                         seq_slot, seq_pos0, seq_qstart, seq_qlen, sink, M, B, H, rank, rot, page_size, scale, max_qlen,  \
-                         n_splits, st)
-  if (rank <= 64) return LEB_LM(2);
-  if (rank <= 128) return LEB_LM(4);
-  if (rank <= 256) return LEB_LM(8);
-  return LEB_LM(16);
+#define LEB_LM(NT_, BN_)                                                                                                   \
+  launch_latent_mma<NT_, BN_>((bf16*)out, part, (const bf16*)qt, (const bf16*)qr, (const bf16*)pool, block_table, bt_width, \
+                              seq_slot, seq_pos0, seq_qstart, seq_qlen, sink, M, B, H, rank, rot, page_size, scale, max_qlen,  \
+                              n_splits, st)
+  if (rank <= 64) return LEB_LM(2, 64);
+  if (rank <= 128) return LEB_LM(4, 64);
+  if (rank <= 256) return LEB_LM(8, 64);
+  return LEB_LM(16, 32);         // two stages of 64 rows of up to 768 numbers would not fit beside the queries
 #undef LEB_LM
 }

@@ -602,14 +602,15 @@ def set_latent_mma(on: bool) -> None:
     lib().leb_set_latent_mma(1 if on else 0)
 
 
-def latent_attention_splits(batch, H: int, mma: bool = False) -> int:
+def latent_attention_splits(batch, H: int, mma: bool = False, rank: int = 0) -> int:
     """Pieces the key range of a decode step is cut into so that the blocks fill the SMs (1 for prompts).
     The tensor-core kernel takes up to 64 heads in a block that is alone on its SM, the general one 8 in
-    blocks of which an SM holds several; a piece is at least four tiles of 32 cached rows."""
+    blocks of which an SM holds several; a piece is at least four tiles of cached rows (32, or 64 in the
+    tensor-core kernel for latents up to 256)."""
     if batch.max_qlen != 1:
         return 1
     blocks = batch.n_seqs * -(-H // (64 if mma else 8))
-    tiles = -(-batch.max_kvlen // 32)
+    tiles = -(-batch.max_kvlen // (64 if mma and rank <= 256 else 32))
     want = max(1, ((1 if mma else 2) * sm_count()) // max(1, blocks))
     return int(max(1, min(want, tiles // 4, 64)))
 
@@ -836,6 +837,22 @@ def _attention_decode_raw(out, raw: RawQKV, k_pool, v_pool, block_table, batch, 
 # ----------------------------------------------------------------------------------------------
 STORE, ACCUMULATE, SWIGLU = 0, 1, 2
 GEGLU = SWIGLU | (GELU_TANH << 8)     # the gated epilogue with the tanh form of gelu: the activation rides in the upper bits
+CLAMPED_SIGMOID_SLOPE = 1.702     # the slope the fused form of the clamped activation is built with
+
+
+def gated_epilogue(act: int, limit: float = 0.0, alpha: float = 1.0) -> int | None:
+    """The epilogue code of a bfloat16 product that applies act(gate) * up itself, or None where the
+    activation has no fused form (the clamped one with another slope, or a limit bfloat16 does not hold
+    exactly: the limit travels in the code as the upper half of its float)."""
+    if act in (SILU, GELU_TANH):
+        return SWIGLU | (act << 8)
+    if act == CLAMPED_SIGMOID and alpha == CLAMPED_SIGMOID_SLOPE and limit > 0:
+        bits = int(torch.tensor(float(limit), dtype=torch.float32).view(torch.int32))
+        if bits & 0xFFFF == 0:
+            return SWIGLU | (CLAMPED_SIGMOID << 8) | ((bits >> 16) << 16)
+    return None
+
+
 SMALL_M = 16  # rows up to which the weight-streaming kernel is used; above, tcgen05 tiles
 
 

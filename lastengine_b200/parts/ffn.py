@@ -133,9 +133,10 @@ class SigmoidTopKMoE(FeedForward):
 
     def load(self, tensors, env: BuildEnv) -> None:
         n = self.n
-        # the products' gated epilogue knows silu and gelu; another activation runs as a kernel of its own
-        self.fused = (not env.is_float32) and self.Fe % 16 == 0 and self.act in (kernels.SILU, kernels.GELU_TANH)
-        self.epilogue = kernels.SWIGLU | (self.act << 8)
+        # the products' gated epilogue knows silu, gelu and the clamped form with the slope 1.702 and a limit
+        # that bfloat16 holds exactly; anything else runs as a kernel of its own on the float gate and up values
+        self.epilogue = kernels.gated_epilogue(self.act, self.limit, self.alpha)
+        self.fused = (not env.is_float32) and self.Fe % 16 == 0 and self.D % 8 == 0 and self.epilogue is not None
         self.router_w = tensors[n["router"]].contiguous()
         self.router_b = tensors[n["bias"]].contiguous() if self.use_bias else None
         self.w13 = torch.stack([fuse_gate_up(tensors[n["gate"].format(e=e)], tensors[n["up"].format(e=e)],

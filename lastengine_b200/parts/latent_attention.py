@@ -159,7 +159,7 @@ class LatentAttentionMixer(Mixer):
         kernels.linear(qt.view(H * M, rank), qn.view(H * M, self.hd_p), self.w_ukt, group_offsets=offsets, rows_hint=H * M)
         u = ws.get("lat.u", (H, M, self.rank_p), env.dtype)
         mma = kernels.latent_attention_uses_mma(env.dtype, rank, rd, cache.page_size, self.rank_p)
-        n_splits = kernels.latent_attention_splits(batch, H, mma)
+        n_splits = kernels.latent_attention_splits(batch, H, mma, rank)
         scratch = ws.get("lat.part", (M * H * n_splits * (rank + 2),), torch.float32) if n_splits > 1 else None
         kernels.latent_attention(u, qt, qr, pool, cache.block_table, batch, self.sink, rank, rd, cache.page_size,
                                  self.scale, n_splits=n_splits, scratch=scratch)

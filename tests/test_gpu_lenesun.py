@@ -103,6 +103,65 @@ def test_clamped_expert_activation(dtype):
     assert H.rel_err(out, want) < (1e-6 if dtype == "float32" else 5e-3)
 
 
+@pytest.mark.parametrize("M,Kd,F", [(1, 64, 48), (8, 96, 160), (16, 256, 512), (40, 128, 256), (128, 256, 2048),
+                                   (300, 64, 96), (700, 512, 1024), (1100, 256, 4096)])
+def test_clamped_activation_as_the_epilogue_of_every_bfloat16_product(M, Kd, F):
+    """Rows from one to over a thousand reach the weight stream, the sliced and the tiled tensor-core products
+    and the one on pairs of SMs; each clamps, applies g sigmoid(1.702 g) (u + 1) and stores."""
+    from lastengine_b200.parts.ffn import fuse_gate_up
+    kk = K()
+    g = torch.Generator().manual_seed(M)
+    x = P.round_bf16(torch.randn(M, Kd, generator=g, dtype=torch.float64))
+    wg = P.round_bf16(torch.randn(F, Kd, generator=g, dtype=torch.float64) * (2.0 / Kd ** 0.5))
+    wu = P.round_bf16(torch.randn(F, Kd, generator=g, dtype=torch.float64) * (2.0 / Kd ** 0.5))
+    w = fuse_gate_up(wg.to(DEV, torch.bfloat16), wu.to(DEV, torch.bfloat16), True)
+    for limit in (1.5, 0.75):
+        epi = kk.gated_epilogue(kk.CLAMPED_SIGMOID, limit, 1.702)
+        assert epi is not None
+        gt = torch.clamp(x @ wg.T, max=limit)
+        up = torch.clamp(x @ wu.T, -limit, limit)
+        want = gt * torch.sigmoid(1.702 * gt) * (up + 1)
+        assert ((x @ wg.T) > limit).any() and ((x @ wu.T) < -limit).any()
+        for dt, tol in ((torch.bfloat16, 8e-3), (torch.float32, 3e-4)):
+            out = torch.zeros(M, F, dtype=dt, device=DEV)
+            kk.linear(out, x.to(DEV, torch.bfloat16), w, epi)
+            kk.check_device_status()
+            assert H.rel_err(out, want) < tol
+    # no fused form for a limit bfloat16 does not hold, or another slope: the part then runs the kernel of its own
+    assert kk.gated_epilogue(kk.CLAMPED_SIGMOID, 1.3, 1.702) is None and kk.gated_epilogue(kk.CLAMPED_SIGMOID, 1.5, 1.0) is None
+
+
+def test_grouped_clamped_epilogue_equals_the_unfused_path():
+    """The expert layer with the fused epilogue (limit 1.5) and with the kernel of its own (limit 1.3) against
+    the plain experts, for a prompt's rows and a decode step's."""
+    from lastengine_b200.engine.workspace import Workspace
+    from lastengine_b200.parts.base import BuildEnv
+    from lastengine_b200.registry import FEED_FORWARDS
+    from lastengine_b200.weights.random_init import random_tensor
+    D, E, k, F = 64, 6, 2, 48
+    for limit, fused in ((1.5, True), (1.3, False)):
+        names = {"router": "router", "bias": "router.b", "gate": "e{e}.gate", "up": "e{e}.up", "down": "e{e}.down"}
+        part = FEED_FORWARDS.get("topk_moe")(hidden_size=D, num_experts=E, top_k=k, expert_size=F, router="softmax_chosen",
+                                             activation="clamped_sigmoid", limit=limit, alpha=1.702, names=names)
+        plain_t = {n: random_tensor(n, sp, 3, 0.3).to(torch.bfloat16).double() for n, sp in part.tensors().items()}
+        plain_t["router"] = plain_t["router"] * 3.0          # logits well apart
+        dev = torch.device(DEV)
+        env = BuildEnv(device=dev, dtype=torch.bfloat16, workspace=Workspace(dev))
+        from lastengine_b200.weights.loader import kept_dtype
+        part.load({n: v.float().to(dev, kept_dtype(part.tensors()[n], torch.bfloat16, torch.bfloat16)) for n, v in plain_t.items()}, env)
+        assert part.fused == fused
+        f = {"router": {"experts": E, "top": k}, "expert": {"ff": F, "limit": limit}}
+        for M in (3, 200):
+            h = inputs(M, D, 60 + M, True)
+            out = torch.zeros(M, D, dtype=torch.float32, device=DEV)
+            part.forward(h.to(DEV, torch.bfloat16), out, False, None, env)
+            margins = []
+            want = P.moe(h, plain_t, f, P.round_bf16, margins)
+            ok = margins[0] > 2e-2
+            assert ok.float().mean() > 0.7
+            assert H.rel_err(out[ok.to(DEV)], want[ok]) < H.TOL_BF16
+
+
 # ---- a mixer alone: its own cache, steps laid out as the engine lays them out ----------------------
 class MixerRig:
     def __init__(self, params, dtype, seed=0, std=0.3, max_tokens=2048, max_seqs=6, edit=None):
