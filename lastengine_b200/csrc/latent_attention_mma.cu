@@ -7,7 +7,7 @@
 // range.  Cached rows [c | k^r] come in tiles of BN = 64 (32 for latents beyond 256) through two shared-memory
 // stages filled by asynchronous copies, the next tile travelling under the current one's products.  Per tile:
 //   S = Q K^T        64 x BN over rank + rot     warp (m-tile of 16 vectors, half of the keys), mma.sync m16n8k16
-//   softmax          float: a warp per 8 vectors, a lane per key; running maximum and sum in registers
+//   softmax          float: four threads per vector, a quarter of the keys each; running maximum and sum in registers
 //   O = O corr + P V 64 x rank over the BN keys  warp (32 vectors, a quarter of the latent), P as bfloat16,
 //                    V = the first `rank` numbers of the same staged rows, read transposed by ldmatrix
 // The accumulators of O (64 x rank floats, 128 registers a thread at rank 512) are why the latent is
@@ -55,7 +55,8 @@ latent_attention_mma_kernel(bf16* __restrict__ out, float* __restrict__ part, co
   const int b = blockIdx.z / n_splits, split = blockIdx.z % n_splits;
   const int slot = seq_slot[b];
   const int qlen = seq_qlen[b];
-  const int row_lo = blockIdx.x * QT;
+  // the last rows of a prompt look back over the most keys: their blocks go first, the short ones fill the end
+  const int row_lo = (gridDim.x - 1 - blockIdx.x) * QT;
   if (row_lo >= qlen) return;
   const int nrows = min(QT, qlen - row_lo);
   const int nheads = min(HC, H - hc * HC);
@@ -138,9 +139,10 @@ latent_attention_mma_kernel(bf16* __restrict__ out, float* __restrict__ part, co
     for (int n = 0; n < NT; n++)
 #pragma unroll
       for (int e = 0; e < 4; e++) o[a][n][e] = 0.f;
-  float mx[8], l[8];                         // of vectors 8 * warp + rr (the same in every lane)
-#pragma unroll
-  for (int rr = 0; rr < 8; rr++) { mx[rr] = LM_NEG; l[rr] = 0.f; }
+  // softmax: four threads per query vector (vector tid / 4), each with a quarter of the tile's keys; the
+  // running maximum and sum of the vector live in all four
+  const int sm_r = tid >> 2, sm_q = tid & 3;
+  float mx = LM_NEG, l = 0.f;
 
   const int g = lane >> 2, tg = lane & 3;
   // S: this warp's 16 vectors and half of the tile's keys;  O: this warp's 32 vectors and quarter of the latent
@@ -161,8 +163,9 @@ latent_attention_mma_kernel(bf16* __restrict__ out, float* __restrict__ part, co
     const int key0 = tile * LM_BN;
     const uint32_t k_base = lm_smem(k_s + (size_t)stage * LM_BN * LDK);
 
-    // ---- S = Q K^T ----  (even and odd slices of the inner size in accumulators of their own: with two
-    // warps per scheduler the products of one accumulator chain would wait for one another)
+    // ---- S = Q K^T ----  Even and odd slices of the inner size sum in accumulators of their own, and a slice's
+    // fragments are asked for before the products of the slice before it are issued: with two warps per
+    // scheduler nothing else hides the way from shared memory or from one product to the next on its chain.
     if (16 * s_mt < R) {
       float s[2][KW / 8][4];
 #pragma unroll
@@ -171,18 +174,32 @@ latent_attention_mma_kernel(bf16* __restrict__ out, float* __restrict__ part, co
         for (int nt = 0; nt < KW / 8; nt++)
 #pragma unroll
           for (int e = 0; e < 4; e++) s[c][nt][e] = 0.f;
-      for (int ks = 0; ks < dk; ks += 32) {
+      uint32_t a0[4], b0[KW / 16][4], a1[4], b1[KW / 16][4];
+      lm_ldsm4(a0, q_addr);
 #pragma unroll
-        for (int c = 0; c < 2; c++) {
-          if (ks + 16 * c >= dk) break;
-          uint32_t a[4];
-          lm_ldsm4(a, q_addr + (ks + 16 * c) * 2);
+      for (int np = 0; np < KW / 16; np++) lm_ldsm4(b0[np], k_base + kb_off + (uint32_t)(np * 16 * LDK * 2));
+      for (int ks = 0; ks < dk; ks += 32) {
+        const bool odd = ks + 16 < dk, more = ks + 32 < dk;
+        if (odd) {
+          lm_ldsm4(a1, q_addr + (ks + 16) * 2);
+#pragma unroll
+          for (int np = 0; np < KW / 16; np++) lm_ldsm4(b1[np], k_base + kb_off + (uint32_t)(np * 16 * LDK * 2) + (ks + 16) * 2);
+        }
+#pragma unroll
+        for (int np = 0; np < KW / 16; np++) {
+          lm_mma(s[0][2 * np], a0, b0[np][0], b0[np][1]);
+          lm_mma(s[0][2 * np + 1], a0, b0[np][2], b0[np][3]);
+        }
+        if (more) {
+          lm_ldsm4(a0, q_addr + (ks + 32) * 2);
+#pragma unroll
+          for (int np = 0; np < KW / 16; np++) lm_ldsm4(b0[np], k_base + kb_off + (uint32_t)(np * 16 * LDK * 2) + (ks + 32) * 2);
+        }
+        if (odd) {
 #pragma unroll
           for (int np = 0; np < KW / 16; np++) {
-            uint32_t bb[4];
-            lm_ldsm4(bb, k_base + kb_off + (uint32_t)(np * 16 * LDK * 2) + (ks + 16 * c) * 2);
-            lm_mma(s[c][2 * np], a, bb[0], bb[1]);
-            lm_mma(s[c][2 * np + 1], a, bb[2], bb[3]);
+            lm_mma(s[1][2 * np], a1, b1[np][0], b1[np][1]);
+            lm_mma(s[1][2 * np + 1], a1, b1[np][2], b1[np][3]);
           }
         }
       }
@@ -201,29 +218,41 @@ latent_attention_mma_kernel(bf16* __restrict__ out, float* __restrict__ part, co
     }
     __syncthreads();
 
-    // ---- softmax over the tile's keys, a lane per key (two keys with tiles of 64) ----
+    // ---- softmax over the tile's keys: thread (vector, quarter) takes keys 8 q .. 8 q + 7 of every 32 (the
+    // rows of S are 1 mod 32 words apart, so the 8 vectors x 4 quarters of a warp meet 32 different banks) ----
+    {
+      float sv[BN / 4];
+      float tmax = LM_NEG;
 #pragma unroll
-    for (int rr = 0; rr < 8; rr++) {
-      const int r = 8 * warp + rr;
-      if (r >= R) break;
-      float sv[BN / 32], p[BN / 32];
-      float tmax = LM_NEG, tsum = 0.f;
+      for (int c = 0; c < BN / 32; c++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          sv[8 * c + j] = sm_r < R ? s_s[sm_r * LDS + 32 * c + 8 * sm_q + j] : LM_NEG;
+          tmax = fmaxf(tmax, sv[8 * c + j]);
+        }
+      tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+      tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+      const float mn = fmaxf(mx, tmax);
+      float tsum = 0.f;
 #pragma unroll
       for (int c = 0; c < BN / 32; c++) {
-        sv[c] = s_s[r * LDS + lane + 32 * c];
-        tmax = fmaxf(tmax, sv[c]);
-      }
-      const float mn = fmaxf(mx[rr], warp_max(tmax));
+        uint32_t pk[4];
 #pragma unroll
-      for (int c = 0; c < BN / 32; c++) {
-        p[c] = sv[c] > 0.5f * LM_NEG ? expf(sv[c] - mn) : 0.f;
-        tsum += p[c];
-        p_s[r * LDP + lane + 32 * c] = __float2bfloat16_rn(p[c]);
+        for (int j = 0; j < 8; j += 2) {
+          const float p0 = sv[8 * c + j] > 0.5f * LM_NEG ? expf(sv[8 * c + j] - mn) : 0.f;
+          const float p1 = sv[8 * c + j + 1] > 0.5f * LM_NEG ? expf(sv[8 * c + j + 1] - mn) : 0.f;
+          tsum += p0 + p1;
+          __nv_bfloat162 two = __floats2bfloat162_rn(p0, p1);
+          pk[j >> 1] = *reinterpret_cast<uint32_t*>(&two);
+        }
+        *reinterpret_cast<uint4*>(p_s + sm_r * LDP + 32 * c + 8 * sm_q) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
-      const float corr = expf(mx[rr] - mn);
-      l[rr] = l[rr] * corr + warp_sum(tsum);
-      mx[rr] = mn;
-      if (lane == 0) c_s[r] = corr;
+      tsum += __shfl_xor_sync(0xffffffffu, tsum, 1);
+      tsum += __shfl_xor_sync(0xffffffffu, tsum, 2);
+      const float corr = expf(mx - mn);
+      l = l * corr + tsum;
+      mx = mn;
+      if (sm_q == 0) c_s[sm_r] = corr;
     }
     __syncthreads();
 
@@ -233,26 +262,35 @@ latent_attention_mma_kernel(bf16* __restrict__ out, float* __restrict__ part, co
       const int r0 = 32 * o_mh + 16 * mt;
       if (r0 >= R) break;
       const float ca = c_s[r0 + g], cb = c_s[r0 + g + 8];
+      if (ca != 1.f || cb != 1.f) {          // once a vector's maximum has settled its sums stay as they are
 #pragma unroll
-      for (int n = 0; n < NT; n++) {
-        o[mt][n][0] *= ca; o[mt][n][1] *= ca; o[mt][n][2] *= cb; o[mt][n][3] *= cb;
+        for (int n = 0; n < NT; n++) {
+          o[mt][n][0] *= ca; o[mt][n][1] *= ca; o[mt][n][2] *= cb; o[mt][n][3] *= cb;
+        }
       }
     }
+    if (32 * o_mh < R) {
+      const bool two = 32 * o_mh + 16 < R;
 #pragma unroll
-    for (int ks = 0; ks < BN / 16; ks++) {
-      uint32_t a[2][4];
-      lm_ldsm4(a[0], p_addr + ks * 32);
-      lm_ldsm4(a[1], p_addr + 16 * LDP * 2 + ks * 32);
+      for (int ks = 0; ks < BN / 16; ks++) {
+        uint32_t a[2][4], bb[4], bn[4];
+        lm_ldsm4(a[0], p_addr + ks * 32);
+        lm_ldsm4(a[1], p_addr + 16 * LDP * 2 + ks * 32);
+        const uint32_t v_addr = k_base + vb_off + (uint32_t)(ks * 16 * LDK * 2);
+        lm_ldsm4t(bb, v_addr);
 #pragma unroll
-      for (int np = 0; np < (NT + 1) / 2; np++) {
-        if (2 * np >= ntu) break;
-        uint32_t bb[4];
-        lm_ldsm4t(bb, k_base + vb_off + (uint32_t)(ks * 16 * LDK * 2) + np * 32);
+        for (int np = 0; np < NT / 2; np++) {
+          if (np + 1 < NT / 2 && 2 * (np + 1) < ntu) lm_ldsm4t(bn, v_addr + (np + 1) * 32);
+          if (2 * np < ntu) {
+            lm_mma(o[0][2 * np], a[0], bb[0], bb[1]);
+            if (2 * np + 1 < ntu) lm_mma(o[0][2 * np + 1], a[0], bb[2], bb[3]);
+            if (two) {
+              lm_mma(o[1][2 * np], a[1], bb[0], bb[1]);
+              if (2 * np + 1 < ntu) lm_mma(o[1][2 * np + 1], a[1], bb[2], bb[3]);
+            }
+          }
 #pragma unroll
-        for (int mt = 0; mt < 2; mt++) {
-          if (32 * o_mh + 16 * mt >= R) break;
-          lm_mma(o[mt][2 * np], a[mt], bb[0], bb[1]);
-          if (2 * np + 1 < NT && 2 * np + 1 < ntu) lm_mma(o[mt][2 * np + 1], a[mt], bb[2], bb[3]);
+          for (int e = 0; e < 4; e++) bb[e] = bn[e];
         }
       }
     }
@@ -260,25 +298,26 @@ latent_attention_mma_kernel(bf16* __restrict__ out, float* __restrict__ part, co
   __syncthreads();
 
   // ---- the end: the sink joins the denominator, or the split's partial sums go out ----
-#pragma unroll
-  for (int rr = 0; rr < 8; rr++) {
-    const int r = 8 * warp + rr;
-    if (r >= R) break;
+  if (sm_q == 0 && sm_r < R) {
+    const int r = sm_r;
     const int i = r / HC, j = r % HC;
-    if (j >= nheads) { if (lane == 0) c_s[r] = 0.f; continue; }
-    const int h = hc * HC + j;
-    if (n_splits == 1) {
-      const float sk = sink ? sink[h] : LM_NEG;
-      const float mn = fmaxf(mx[rr], sk);
-      const float corr = expf(mx[rr] - mn);
-      const float den = l[rr] * corr + (sink ? expf(sk - mn) : 0.f);
-      if (lane == 0) c_s[r] = den > 0.f ? corr / den : 0.f;
-    } else if (lane == 0) {
-      const size_t m = (size_t)q0 + row_lo + i;
-      float* pp = part + ((m * H + h) * n_splits + split) * (size_t)(rank + 2);
-      pp[0] = mx[rr];
-      pp[1] = l[rr];
-      c_s[r] = 1.f;
+    if (j >= nheads) {
+      c_s[r] = 0.f;
+    } else {
+      const int h = hc * HC + j;
+      if (n_splits == 1) {
+        const float sk = sink ? sink[h] : LM_NEG;
+        const float mn = fmaxf(mx, sk);
+        const float corr = expf(mx - mn);
+        const float den = l * corr + (sink ? expf(sk - mn) : 0.f);
+        c_s[r] = den > 0.f ? corr / den : 0.f;
+      } else {
+        const size_t m = (size_t)q0 + row_lo + i;
+        float* pp = part + ((m * H + h) * n_splits + split) * (size_t)(rank + 2);
+        pp[0] = mx;
+        pp[1] = l;
+        c_s[r] = 1.f;
+      }
     }
   }
   __syncthreads();

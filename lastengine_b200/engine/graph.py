@@ -10,6 +10,8 @@ steps cannot move what a graph points at.
 """
 from __future__ import annotations
 
+import gc
+
 import numpy as np
 import torch
 
@@ -184,10 +186,17 @@ class DecodeGraph:
                 before = kernels.launch_count()
                 g = torch.cuda.CUDAGraph()
                 self.ws.frozen = True
+                # No garbage collection while the stream captures: a collector run that frees an earlier
+                # engine's graphs destroys them through the driver, which is not permitted during a capture
+                # and invalidates it (when the collector runs depends on how many objects the process made).
+                gc_was_on = gc.isenabled()
+                gc.disable()
                 try:
                     with torch.cuda.graph(g):
                         self._run(self.batch)
                 finally:
+                    if gc_was_on:
+                        gc.enable()
                     self.ws.frozen = False
                 self.launches = kernels.launch_count() - before
                 self.graph, self.ws_generation = g, self.ws.generation
