@@ -90,11 +90,39 @@ latent_q_split_kernel(T* __restrict__ qn, T* __restrict__ qr, const T* __restric
   const int m = blockIdx.x;
   const int hw = dim + rot;
   const T* row = q + (size_t)m * H * hw;
-  for (int i = threadIdx.x; i < H * dim_p; i += blockDim.x) {
-    const int h = i / dim_p, d = i - h * dim_p;
-    qn[((size_t)h * M + m) * dim_p + d] = d < dim ? row[h * hw + d] : from_f32<T>(0.f);
+  constexpr int PER = 16 / (int)sizeof(T);          // elements of a 16-byte piece
+  if (dim_p == dim && dim % PER == 0 && hw % PER == 0 && (((uintptr_t)q | (uintptr_t)qn) & 15) == 0) {
+    const int pieces = dim / PER;
+    for (int i = threadIdx.x; i < H * pieces; i += blockDim.x) {
+      const int h = i / pieces, c = i - h * pieces;
+      reinterpret_cast<uint4*>(qn + ((size_t)h * M + m) * dim)[c] = reinterpret_cast<const uint4*>(row + h * hw)[c];
+    }
+  } else {
+    for (int i = threadIdx.x; i < H * dim_p; i += blockDim.x) {
+      const int h = i / dim_p, d = i - h * dim_p;
+      qn[((size_t)h * M + m) * dim_p + d] = d < dim ? row[h * hw + d] : from_f32<T>(0.f);
+    }
   }
   const float pos = (float)row_pos[m];
+  if (rot % 2 == 0) {       // a thread per pair: one sine and cosine for both numbers
+    const int hp = rot / 2;
+    for (int i = threadIdx.x; i < H * hp; i += blockDim.x) {
+      const int h = i / hp, t = i - h * hp;
+      const T* r = row + h * hw + dim + 2 * t;
+      float u = to_f32(r[0]), v = to_f32(r[1]);
+      if (2 * t < rot_dims) {
+        const float a = pos * inv_freq[t];
+        const float c = cosf(a), sn = sinf(a);
+        const float u2 = u * c - v * sn;
+        v = v * c + u * sn;
+        u = u2;
+      }
+      T* o = qr + ((size_t)m * H + h) * rot + 2 * t;
+      o[0] = from_f32<T>(u);
+      o[1] = from_f32<T>(v);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < H * rot; i += blockDim.x) {
     const int h = i / rot, d = i - h * rot;
     const T* r = row + h * hw + dim;
@@ -107,9 +135,9 @@ latent_q_split_kernel(T* __restrict__ qn, T* __restrict__ qr, const T* __restric
   }
 }
 
-// in [H, M, w] -> out [M, H * w]
-template <typename T>
-__global__ void heads_to_rows_kernel(T* __restrict__ out, const T* __restrict__ in, int M, int H, int w) {
+// in [H, M, w] -> out [M, H * w], one piece per thread: an element, or 16 bytes where the rows allow it
+template <typename P>
+__global__ void heads_to_rows_kernel(P* __restrict__ out, const P* __restrict__ in, int M, int H, int w) {
   pdl_wait();
   const size_t total = (size_t)M * H * w;
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -356,13 +384,20 @@ LEB_API int leb_latent_q_split(void* qn, void* qr, const void* q, int dtype, con
 }
 
 LEB_API int leb_heads_to_rows(void* out, const void* in, int dtype, int M, int H, int w, cudaStream_t st) {
-  const size_t total = (size_t)M * H * w;
-  if (total == 0) return 0;
+  if ((size_t)M * H * w == 0) return 0;
+  LEB_REQUIRE(dtype == LEB_F32 || dtype == LEB_BF16, "leb_heads_to_rows: unknown dtype %d", dtype);
   LebPlainLaunches plain(true);
-  const dim3 grid((unsigned)((total + 255) / 256)), block(256);
-  if (dtype == LEB_F32) leb_launch(heads_to_rows_kernel<float>, grid, block, 0, st, (float*)out, (const float*)in, M, H, w);
-  else if (dtype == LEB_BF16) leb_launch(heads_to_rows_kernel<bf16>, grid, block, 0, st, (bf16*)out, (const bf16*)in, M, H, w);
-  else return leb_fail("leb_heads_to_rows: unknown dtype %d", dtype);
+  const int per16 = dtype == LEB_F32 ? 4 : 8;      // elements of a 16-byte piece
+  if (w % per16 == 0 && (((uintptr_t)out | (uintptr_t)in) & 15) == 0) {
+    const size_t total = (size_t)M * H * (w / per16);
+    leb_launch(heads_to_rows_kernel<uint4>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, (uint4*)out,
+               (const uint4*)in, M, H, w / per16);
+  } else {
+    const size_t total = (size_t)M * H * w;
+    const dim3 grid((unsigned)((total + 255) / 256)), block(256);
+    if (dtype == LEB_F32) leb_launch(heads_to_rows_kernel<float>, grid, block, 0, st, (float*)out, (const float*)in, M, H, w);
+    else leb_launch(heads_to_rows_kernel<bf16>, grid, block, 0, st, (bf16*)out, (const bf16*)in, M, H, w);
+  }
   LEB_CHECK_LAUNCH("leb_heads_to_rows");
   return 0;
 }

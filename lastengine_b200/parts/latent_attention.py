@@ -165,6 +165,9 @@ class LatentAttentionMixer(Mixer):
                                  self.scale, n_splits=n_splits, scratch=scratch)
         v = ws.get("lat.v", (H, M, vd), env.dtype)
         kernels.linear(v.view(H * M, vd), u.view(H * M, self.rank_p), self.w_uv, group_offsets=offsets, rows_hint=H * M)
-        o = ws.get("lat.o", (M, H * vd), env.dtype)
-        kernels.heads_to_rows(o, v)
+        if M == 1:
+            o = v.view(1, H * vd)                  # one row: head-major and row-major are the same memory
+        else:
+            o = ws.get("lat.o", (M, H * vd), env.dtype)
+            kernels.heads_to_rows(o, v)
         kernels.linear(out, o, self.w_o, kernels.ACCUMULATE if accumulate else kernels.STORE)
