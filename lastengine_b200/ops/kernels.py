@@ -605,14 +605,13 @@ def set_latent_mma(on: bool) -> None:
 def latent_attention_splits(batch, H: int, mma: bool = False, rank: int = 0) -> int:
     """Pieces the key range of a decode step is cut into so that the blocks fill the SMs (1 for prompts).
     The tensor-core kernel takes up to 64 heads in a block that is alone on its SM, the general one 8 in
-    blocks of which an SM holds several; a piece is at least four tiles of cached rows (32, or 64 in the
-    tensor-core kernel for latents up to 256)."""
+    blocks of which an SM holds several; a piece is at least 128 cached rows (measured at 2,048 positions:
+    16 pieces of 128 rows are the fastest cut at batch 1 and 8 for latents of 256 and of 512)."""
     if batch.max_qlen != 1:
         return 1
     blocks = batch.n_seqs * -(-H // (64 if mma else 8))
-    tiles = -(-batch.max_kvlen // (64 if mma and rank <= 256 else 32))
     want = max(1, ((1 if mma else 2) * sm_count()) // max(1, blocks))
-    return int(max(1, min(want, tiles // 4, 64)))
+    return int(max(1, min(want, batch.max_kvlen // 128, 64)))
 
 
 def latent_attention(out: torch.Tensor, qt: torch.Tensor, qr: torch.Tensor, pool: torch.Tensor, block_table, batch,
